@@ -7,6 +7,7 @@ from ..parts.registry import register_architecture
 from ..parts.spec import BlockSpec, ModelSpec, PartSpec, RunStep
 from .bivizen_config import BivizenConfig
 from .model_config import Qwen2Config
+from .pefivik_config import PefivikConfig
 from .tomodra_config import TomodraConfig
 
 
@@ -142,3 +143,61 @@ def tomodra_spec(config: TomodraConfig) -> ModelSpec:
 
 
 register_architecture("Tomodra", TomodraConfig, tomodra_spec)
+
+
+def pefivik_spec(config: PefivikConfig) -> ModelSpec:
+    """Pefivik: the embedding is the token's row plus a row of a second table chosen by a hash of the token and the one
+    before it.  Every layer is a pre-norm block whose sub-layers' outputs are multiplied by one constant before they
+    join the stream, and whose norms have ONE learned number each: x += m mixer(n1(x)); x += m ff(n2(x)).  The mixer is
+    attention over a compressed latent without positions, with a sink in the softmax and a sigmoid gate per head, or
+    HGRN2 (a matrix state per head whose forget gate also says what is written); the feed-forward is a dense one with
+    biases and the PolyNorm activation, or a mixture of gated experts chosen among the best groups, beside a shared
+    expert.  A stretch of layers may run several times over with the same weights, every pass with a cache of its own;
+    ahead of every pass the stream receives a row of the table loop.step, and ahead of every pass but the first the
+    embedding's output once more.  The logits are soft-capped.  Tensors: embed, bigram, loop.step, l<i>.norm1,
+    l<i>.norm2, l<i>.mix.*, l<i>.mlp.*, final.norm, head."""
+    e = config.width
+    norm = PartSpec("rms_scalar", {"size": e, "eps": config.eps, "tensor": ""})
+    layers = []
+    for i, l in enumerate(config.layers):
+        if l.type == "latent_attention":
+            mixer = PartSpec("latent_attention", {
+                "hidden": e, "heads": l.heads, "head_dim": l.dim, "rot_dim": 0, "v_dim": l.vdim, "kv_rank": l.kv_rank,
+                "scale": l.scale, "window": None, "eps": config.eps, "sink": True, "head_gate": True})
+        else:
+            mixer = PartSpec("hgrn2", {"hidden": e, "heads": l.heads, "head_dim": l.dim, "v_dim": l.vdim,
+                                       "eps": config.eps})
+        parts = {"mixer_norm": norm, "mixer": mixer}
+        names = {"mixer_norm": "norm1", "mixer": "mix.", "feed_forward_norm": "norm2", "feed_forward": "mlp."}
+        f = l.mlp
+        if f is not None and f.kind == "dense":
+            parts["feed_forward"] = PartSpec("polynorm_mlp", {"hidden": e, "intermediate": f.ff, "eps": config.eps})
+        elif f is not None:
+            parts["feed_forward"] = PartSpec("routed_experts", {
+                "hidden": e, "experts": f.experts, "top": f.top, "intermediate": f.ff, "shared_intermediate": f.shared_ff,
+                "shared_gate": False, "score": "sigmoid", "renormalize": True, "norm_eps": 1e-20, "route_scale": f.scale,
+                "groups": (f.groups, f.keep) if f.groups > 1 else None, "weight_on": "output"})
+        if f is not None:
+            parts["feed_forward_norm"] = norm
+        params = {"residual_scale": config.residual_mult}
+        if f is None and l.second_norm:
+            params["idle"] = (("norm2", ()),)      # a tensor of the file that the layer does not use
+        layers.append(BlockSpec(kind="pre_norm", prefix=f"l{i}.", parts=parts, names=names, params=params))
+    order = [RunStep(i) for i in range(config.loop_start)]
+    tables = (("loop.step", config.loop_times),) if config.has_loop else ()
+    if config.loops:
+        for t in range(config.loop_times):
+            order += [RunStep(i, add_embedding=(t > 0 and i == config.loop_start),
+                              add_row=("loop.step", t) if i == config.loop_start else None)
+                      for i in range(config.loop_start, config.loop_stop)]
+    order += [RunStep(i) for i in range(config.loop_stop if config.loops else config.loop_start, len(layers))]
+    return ModelSpec(
+        architecture=config.architecture, hidden_size=e, vocab_size=config.vocab, max_positions=config.max_positions,
+        layers=tuple(layers), order=tuple(order), final_norm=norm, embedding_name="embed", final_norm_prefix="final.norm",
+        output_name="head", eos_token_id=config.eos_token_id, logit_softcap=config.logit_softcap,
+        embedding=PartSpec("bigram_hash", {"vocab": config.vocab, "hidden": e, "buckets": config.buckets,
+                                           "mul_prev": config.mul_prev, "mul_cur": config.mul_cur, "pairs": "bigram"}),
+        stream_tables=tables)
+
+
+register_architecture("Pefivik", PefivikConfig, pefivik_spec)

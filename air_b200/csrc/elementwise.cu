@@ -30,6 +30,84 @@ __global__ void embedding_kernel(const TT* __restrict__ table, const int* __rest
         out[(size_t)t * E + i] = ok ? (multiplier == 1.f ? to_float(row[i]) : to_float(row[i]) * multiplier) : 0.f;
 }
 
+// ---------------------------------------------------------------- embedding with a table of token pairs
+// out[t, :] = table[id_t, :] + pairs[r_t, :] (float32), r_t = (prev_t * mul_prev + id_t * mul_cur) mod buckets, and
+// r_t = buckets (the table's last row) at position 0 of a request.  prev_t is the id of the row above where that row
+// belongs to the same request (equal slot: a request appears once in a step), else previous[slot], which the step
+// that brought the request's last tokens left there (remember_tokens_kernel, below, run after this kernel: the two
+// are apart because the block of an entry's first row reads what the block of its last row would overwrite).
+// Ids -(s+1) are resolved as in embedding_kernel; resolved[t] receives the id that was used.  out2, if given, is a
+// second copy of the rows.  Rows of padding (slot < 0) become zeros.
+template <typename TT>
+__global__ void bigram_embedding_kernel(const TT* __restrict__ table, const TT* __restrict__ pairs,
+                                        const int* __restrict__ ids, const int* __restrict__ positions,
+                                        const int* __restrict__ token_seq, const int* __restrict__ previous,
+                                        const int* __restrict__ last_token, float* __restrict__ out,
+                                        float* __restrict__ out2, int* __restrict__ resolved, int E, int V,
+                                        long long buckets, long long mul_prev, long long mul_cur, int* status) {
+    pdl_wait();          // the step's first kernel: see embedding_kernel
+    pdl_trigger();
+    trace_point(TR_EMBED);
+    const int t = blockIdx.x;
+    const int slot = token_seq[t];
+    if (slot < 0) {      // padding: rows of zeros, so that whatever reads them reads numbers
+        for (int i = threadIdx.x; i < E; i += blockDim.x) {
+            out[(size_t)t * E + i] = 0.f;
+            if (out2) out2[(size_t)t * E + i] = 0.f;
+        }
+        if (threadIdx.x == 0) resolved[t] = 0;
+        return;
+    }
+    int id = ids[t];
+    if (id < 0 && last_token) id = last_token[-id - 1];
+    const bool ok = id >= 0 && id < V;
+    if (!ok && threadIdx.x == 0 && status) atomicExch(status, 1);
+    if (threadIdx.x == 0) resolved[t] = ok ? id : 0;
+    long long r = buckets;
+    if (positions[t] > 0) {
+        int prev;
+        if (t > 0 && token_seq[t - 1] == slot) {
+            prev = ids[t - 1];
+            if (prev < 0 && last_token) prev = last_token[-prev - 1];
+        } else {
+            prev = previous[slot];
+        }
+        if (prev < 0 || prev >= V) prev = 0;
+        r = ((long long)prev * mul_prev + (long long)(ok ? id : 0) * mul_cur) % buckets;
+    }
+    const TT* row = table + (size_t)(ok ? id : 0) * E;
+    const TT* pair = pairs + (size_t)r * E;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        const float x = ok ? to_float(row[i]) + to_float(pair[i]) : 0.f;
+        out[(size_t)t * E + i] = x;
+        if (out2) out2[(size_t)t * E + i] = x;
+    }
+}
+
+// previous[slots[e]] = resolved[q_start[e + 1] - 1]: the last token of every entry, for the request's next step.
+__global__ void remember_tokens_kernel(const int* __restrict__ resolved, const int* __restrict__ q_start,
+                                       const int* __restrict__ slots, int* __restrict__ previous, int S) {
+    pdl_enter(TR_EMBED);
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= S) return;
+    const int slot = slots[e];
+    if (slot < 0 || q_start[e + 1] <= q_start[e]) return;
+    previous[slot] = resolved[q_start[e + 1] - 1];
+}
+
+// ---------------------------------------------------------------- h += again + row
+// h[t, i] += again[t, i] + row[i] (each optional): what a run adds to the stream ahead of its layer.
+__global__ void stream_add_kernel(float* __restrict__ h, const float* __restrict__ again, const float* __restrict__ row,
+                                  int E, size_t n) {
+    pdl_enter(TR_NORM);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float x = h[i];
+        if (again) x += again[i];
+        if (row) x += row[i % E];
+        h[i] = x;
+    }
+}
+
 // ---------------------------------------------------------------- h += delta
 // h[t, i] += sum over parts of delta[part, t, i], the parts added in order (float32 stream; delta float32
 // or bfloat16).  The norm kernel below does this sum on its way; this is the sum alone, for a norm of
@@ -725,6 +803,31 @@ AIR_API int air_embedding(const void* table, int table_dtype, const int* ids, co
     AIR_DISPATCH(table_dtype, TT, return launch(embedding_kernel<TT>, T, 256, 0, stream, (const TT*)table, ids,
                                                 last_token, out, E, V, multiplier, status));
     return 0;
+}
+
+AIR_API int air_bigram_embedding(const void* table, const void* pairs, int table_dtype, const int* ids,
+                                 const int* positions, const int* token_seq, const int* previous,
+                                 const int* last_token, float* out, float* out2, int* resolved, int T, int E, int V,
+                                 long long buckets, long long mul_prev, long long mul_cur, int* status,
+                                 cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (buckets <= 0 || mul_prev < 0 || mul_cur < 0 || !previous || !resolved) return AIR_ERR_BAD_ARGUMENT;
+    AIR_DISPATCH(table_dtype, TT, return launch(bigram_embedding_kernel<TT>, T, 256, 0, stream, (const TT*)table,
+                                                (const TT*)pairs, ids, positions, token_seq, previous, last_token, out,
+                                                out2, resolved, E, V, buckets, mul_prev, mul_cur, status));
+    return 0;
+}
+
+AIR_API int air_remember_tokens(const int* resolved, const int* q_start, const int* slots, int* previous, int S,
+                                cudaStream_t stream) {
+    if (S <= 0) return 0;
+    return launch(remember_tokens_kernel, (S + 127) / 128, 128, 0, stream, resolved, q_start, slots, previous, S);
+}
+
+AIR_API int air_stream_add(float* h, const float* again, const float* row, int E, long long n, cudaStream_t stream) {
+    if (n <= 0 || (!again && !row)) return 0;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    return launch(stream_add_kernel, blocks, 256, 0, stream, h, again, row, E, (size_t)n);
 }
 
 AIR_API int air_add_parts(float* h, const void* delta, int delta_dtype, int parts, long long n, cudaStream_t stream) {

@@ -9,9 +9,46 @@
 //                       the partial sums of a split product, [parts, T, E], which are added in order), written back into
 //                       the stream h when no rows are named, and out = x / sqrt(mean(x^2) + eps) * w.  With `rows`
 //                       the kernel reads h[rows[r]] and leaves h alone.  Without w it only completes the stream.
+//   polynorm_kernel     out[t, :] = a N(z) + b N(z^2) + c N(z^3) + e over a token's F values z = in[t, :] + bias, powers
+//                       taken per element and N(u) = u / sqrt(mean(u^2) + eps); 32-bit, written in out's type.  out has
+//                       ldo >= F columns: column F (if any) receives 1 and the ones behind it 0, so that a product
+//                       whose matrix holds a bias in column F adds that bias.
 #include "common.cuh"
 
 namespace air {
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+polynorm_kernel(const float* __restrict__ in, int ld, const float* __restrict__ bias, TO* __restrict__ out, int ldo,
+                int F, float a, float b, float c, float e, float eps) {
+    __shared__ float scratch[32];
+    pdl_enter(TR_GLU);
+    const int t = blockIdx.x;
+    const float* row = in + (size_t)t * ld;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    for (int i = threadIdx.x; i < F; i += blockDim.x) {
+        const float z = row[i] + (bias ? bias[i] : 0.f);
+        const float z2 = z * z;
+        s2 += z2;
+        s4 = fmaf(z2, z2, s4);
+        s6 = fmaf(z2 * z, z2 * z, s6);
+    }
+    s2 = block_sum(s2, scratch);
+    s4 = block_sum(s4, scratch);
+    s6 = block_sum(s6, scratch);
+    const float r1 = a / sqrtf(s2 / (float)F + eps), r2 = b / sqrtf(s4 / (float)F + eps),
+                r3 = c / sqrtf(s6 / (float)F + eps);
+    TO* dst = out + (size_t)t * ldo;
+    for (int i = threadIdx.x; i < ldo; i += blockDim.x) {
+        float y = i == F ? 1.f : 0.f;
+        if (i < F) {
+            const float z = row[i] + (bias ? bias[i] : 0.f);
+            const float z2 = z * z;
+            y = z * r1 + z2 * r2 + z2 * z * r3 + e;
+        }
+        dst[i] = from_float<TO>(y);
+    }
+}
 
 template <typename TI, typename TO>
 __global__ void glu_kernel(const TI* __restrict__ in, TO* __restrict__ out, int I, int block, size_t total,
@@ -90,6 +127,15 @@ AIR_API int air_glu(const void* in, int in_dtype, void* out, int out_dtype, int 
         return air::launch(air::glu_kernel<TI, TO>, blocks, 256, 0, stream, (const TI*)in, (TO*)out, I, block, total,
                            alpha, limit, shift);
     }));
+    return 0;
+}
+
+AIR_API int air_polynorm(const float* in, int ld, const float* bias, void* out, int out_dtype, int ldo, int T, int F,
+                         float a, float b, float c, float e, float eps, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (F <= 0 || ldo < F || ld < F) return AIR_ERR_BAD_ARGUMENT;
+    AIR_DISPATCH(out_dtype, TO, return air::launch(air::polynorm_kernel<TO>, T, 256, 0, stream, in, ld, bias, (TO*)out,
+                                                   ldo, F, a, b, c, e, eps));
     return 0;
 }
 

@@ -11,7 +11,8 @@
 //   with a_local the row slot - (the group's first slot); plus g * a_group_stride elements.
 //   Where a slot's row of C goes: with o_index, p = o_index[slot]: part p % o_div, row p / o_div of out
 //   [o_div, rows, N] (o_part_stride elements per part); else row `slot` (or, o_local, the row inside the group) plus
-//   g * o_group_stride.
+//   g * o_group_stride.  With o_scale (and o_index) the row of C is multiplied by o_scale[o_index[slot]] in 32-bit
+//   before it is written (the weight of a token's choice on the expert's OUTPUT).
 //   Epilogue 0: C as float32 or in A's type.  Epilogue 1: W_g is [2 F, K], blocks of gate_block rows of the gate and
 //   as many of the linear branch in turn (gate_block = F: all gate rows, then all linear rows), the arrangement that
 //   the dense gated feed-forward uses; C [rows, F] = silu(gate) * linear in A's type.
@@ -35,6 +36,7 @@ struct GroupedArgs {
     const int* start; int rows_per_group; const int* tiles; const int* num_tiles;
     int N, K;
     int gate_block;      // epilogue 1: rows of W_g come in blocks of gate_block gate rows and as many linear rows in turn
+    const float* o_scale;
 };
 
 constexpr int GG_BM = 64, GG_BN = 64, GG_BK = 16;
@@ -45,7 +47,7 @@ grouped_gemm_kernel(const GroupedArgs p) {
     __shared__ float As[GG_BK][GG_BM + 4];
     __shared__ float Ws[EPI == 1 ? 2 : 1][GG_BK][GG_BN + 4];
     __shared__ long long a_off[GG_BM], o_off[GG_BM];
-    __shared__ float a_mul[GG_BM];
+    __shared__ float a_mul[GG_BM], o_mul[GG_BM];
     pdl_enter(TR_GROUPED_GEMM);
     int g, slot0, first, rows;
     if (p.start) {
@@ -65,7 +67,7 @@ grouped_gemm_kernel(const GroupedArgs p) {
     const int tid = threadIdx.x;
     if (tid < GG_BM) {
         long long a = -1, o = -1;
-        float mul = 1.f;
+        float mul = 1.f, omul = 1.f;
         if (tid < rows) {
             const int slot = slot0 + tid;
             if (p.a_index) {
@@ -78,6 +80,7 @@ grouped_gemm_kernel(const GroupedArgs p) {
             if (p.o_index) {
                 const int dst = p.o_index[slot];
                 o = (long long)(dst % p.o_div) * p.o_part_stride + (long long)(dst / p.o_div) * p.ldo;
+                if (p.o_scale) omul = p.o_scale[dst];
             } else {
                 o = (long long)(p.o_local ? slot - first : slot) * p.ldo + (long long)g * p.o_group_stride;
             }
@@ -85,6 +88,7 @@ grouped_gemm_kernel(const GroupedArgs p) {
         a_off[tid] = a;
         o_off[tid] = o;
         a_mul[tid] = mul;
+        o_mul[tid] = omul;
     }
     __syncthreads();
     const T* A = (const T*)p.A;
@@ -142,6 +146,7 @@ grouped_gemm_kernel(const GroupedArgs p) {
     for (int i = 0; i < 4; ++i) {
         const long long o = o_off[ty * 4 + i];
         if (o < 0) continue;
+        const float om = o_mul[ty * 4 + i];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
@@ -150,9 +155,9 @@ grouped_gemm_kernel(const GroupedArgs p) {
                 const float gate = acc[0][i][j], lin = acc[EPI == 1 ? 1 : 0][i][j];
                 ((T*)p.out)[o + n] = from_float<T>(gate / (1.f + expf(-gate)) * lin);
             } else if (p.out_f32) {
-                ((float*)p.out)[o + n] = acc[0][i][j];
+                ((float*)p.out)[o + n] = acc[0][i][j] * om;
             } else {
-                ((T*)p.out)[o + n] = from_float<T>(acc[0][i][j]);
+                ((T*)p.out)[o + n] = from_float<T>(acc[0][i][j] * om);
             }
         }
     }
@@ -183,7 +188,7 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
     constexpr int TILE = GG_BM * GT_LD;           // elements of one staged tile
     extern __shared__ __align__(16) __nv_bfloat16 staged[];      // [stages][1 + NW][64][GT_LD]
     __shared__ long long a_off[GG_BM], o_off[GG_BM];
-    __shared__ float a_mul[GG_BM];
+    __shared__ float a_mul[GG_BM], o_mul[GG_BM];
     pdl_enter(TR_GROUPED_GEMM);
     int g, slot0, first, rows;
     if (p.start) {
@@ -203,7 +208,7 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
     const int tid = threadIdx.x;
     if (tid < GG_BM) {
         long long a = -1, o = -1;
-        float mul = 1.f;
+        float mul = 1.f, omul = 1.f;
         if (tid < rows) {
             const int slot = slot0 + tid;
             if (p.a_index) {
@@ -216,6 +221,7 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
             if (p.o_index) {
                 const int dst = p.o_index[slot];
                 o = (long long)(dst % p.o_div) * p.o_part_stride + (long long)(dst / p.o_div) * p.ldo;
+                if (p.o_scale) omul = p.o_scale[dst];
             } else {
                 o = (long long)(p.o_local ? slot - first : slot) * p.ldo + (long long)g * p.o_group_stride;
             }
@@ -223,6 +229,7 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
         a_off[tid] = a;
         o_off[tid] = o;
         a_mul[tid] = mul;
+        o_mul[tid] = omul;
     }
     __syncthreads();
     const __nv_bfloat16* A = (const __nv_bfloat16*)p.A;
@@ -308,13 +315,14 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
     for (int half = 0; half < 2; ++half) {
         const long long o = o_off[r0 + gq + 8 * half];
         if (o < 0) continue;
+        const float om = o_mul[r0 + gq + 8 * half];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int n = n0 + 8 * j + 2 * tq + i;
                 if (n >= N) continue;
-                const float v = acc[0][j][2 * half + i];
+                const float v = acc[0][j][2 * half + i] * (EPI == 1 ? 1.f : om);
                 if (EPI == 1) {
                     const float lin = acc[NW - 1][j][2 * half + i];
                     ((__nv_bfloat16*)p.out)[o + n] = __float2bfloat16_rn(v / (1.f + expf(-v)) * lin);
@@ -334,16 +342,16 @@ AIR_API int air_grouped_gemm(const void* A, long long lda, long long a_group_str
                              long long ldo, long long o_group_stride, const int* o_index, int o_div,
                              long long o_part_stride, int o_local, int out_f32, const int* start, int rows_per_group,
                              const int* tiles, const int* num_tiles, int max_tiles, int groups, int N, int K,
-                             int dtype, int epi, int gate_block, cudaStream_t stream) {
+                             int dtype, int epi, int gate_block, const float* o_scale, cudaStream_t stream) {
     if (N <= 0 || K <= 0 || groups <= 0) return 0;
     if ((start != nullptr) != (tiles != nullptr) || (start && !num_tiles) || epi < 0 || epi > 1 ||
-        (a_index && a_div <= 0) || (o_index && o_div <= 0) || (a_scale && !a_index))
+        (a_index && a_div <= 0) || (o_index && o_div <= 0) || (a_scale && !a_index) || (o_scale && (!o_index || epi)))
         return AIR_ERR_BAD_ARGUMENT;
     if (epi == 1 && gate_block <= 0) gate_block = N;
     if (epi == 1 && N % gate_block) return AIR_ERR_BAD_ARGUMENT;
     air::GroupedArgs p{A, lda, a_group_stride, a_index, a_div, a_local, a_scale, W, w_group_stride, out, ldo,
                        o_group_stride, o_index, o_div, o_part_stride, o_local, out_f32, start, rows_per_group, tiles,
-                       num_tiles, N, K, gate_block};
+                       num_tiles, N, K, gate_block, o_scale};
     const int row_tiles = start ? max_tiles : (rows_per_group + air::GG_BM - 1) / air::GG_BM;
     if (row_tiles <= 0) return 0;
     if (row_tiles > 65535 || groups > 65535) return AIR_ERR_BAD_ARGUMENT;

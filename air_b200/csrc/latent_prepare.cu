@@ -6,7 +6,9 @@
 //   with i + rot/2, by the angle position * freq[i] (a 64-bit product, cos and sin taken in 64-bit once per token);
 //   the row [c | kr] goes to the token's place in the pages ([P, R + rot] per page, no heads); the plain part of q goes
 //   to q_plain [T, H, d] (the matrix product that absorbs the key expansion reads it), the rotated part to
-//   q_full[t, h, R : R + rot] (float32; that product fills q_full[t, h, 0 : R]).
+//   q_full[t, h, R : R + rot] (float32; that product fills q_full[t, h, 0 : R]).  rot may be 0 (no rotated parts).
+//   Where the layer gates its heads, proj also holds one logit per head from column gate_col on, and
+//   gate_out[t, h] = sigmoid(logit) (float32).
 //
 // One block per token.
 #include "common.cuh"
@@ -19,7 +21,7 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, const float* __res
                       const double* __restrict__ freq, const int* __restrict__ positions,
                       const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_blocks,
                       TO* __restrict__ q_plain, float* __restrict__ q_full, TO* __restrict__ cache, int owns, int H,
-                      int d, int rot, int R, int P, int* status) {
+                      int d, int rot, int R, int P, float* __restrict__ gate_out, int gate_col, int* status) {
     __shared__ float cs[128], sn[128];
     __shared__ float scratch[32];
     pdl_enter(TR_LATENT_PREPARE);
@@ -48,6 +50,9 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, const float* __res
         dst[j] = u * cs[j] - v * sn[j];
         dst[j + half] = v * cs[j] + u * sn[j];
     }
+    if (gate_out)
+        for (int h = threadIdx.x; h < H; h += blockDim.x)
+            gate_out[(size_t)t * H + h] = 1.f / (1.f + expf(-in[gate_col + h]));
     if (!owns) return;
     const int page = block_table[(size_t)slot * max_blocks + pos / P];
     if (page < 0) {
@@ -73,13 +78,16 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, const float* __res
 AIR_API int air_latent_prepare(const float* proj, int ld, const float* c_w, float eps, const double* freq,
                                const int* positions, const int* token_seq, const int* block_table, int max_blocks,
                                void* q_plain, float* q_full, void* cache, int out_dtype, int owns, int T, int H, int d,
-                               int rot, int R, int P, int* status, cudaStream_t stream) {
+                               int rot, int R, int P, float* gate_out, int gate_col, int* status,
+                               cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (rot < 0 || (rot & 1) || rot > 256 || (rot > 0 && !freq) || (owns && !c_w) || d <= 0 || R <= 0)
+    if (rot < 0 || (rot & 1) || rot > 256 || (rot > 0 && !freq) || (owns && !c_w) || d <= 0 || R <= 0 ||
+        (gate_out && (gate_col < H * (d + rot) + (owns ? R + rot : 0) || gate_col + H > ld)))
         return AIR_ERR_BAD_ARGUMENT;
     AIR_DISPATCH(out_dtype, TO, return air::launch(air::latent_prepare_kernel<TO>, T, 256, 0, stream, proj, ld, c_w, eps,
                                                    freq, positions, token_seq, block_table, max_blocks, (TO*)q_plain,
-                                                   q_full, (TO*)cache, owns, H, d, rot, R, P, status));
+                                                   q_full, (TO*)cache, owns, H, d, rot, R, P, gate_out, gate_col,
+                                                   status));
     return 0;
 }
 

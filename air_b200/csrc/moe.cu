@@ -4,7 +4,10 @@
 // moe_route_kernel: from the router's logits z [T, ld] (float32; the first n columns, and at column n, where the
 //   layer has one, the logit of a gate for a shared expert) to each token's `top` experts with the largest scores.
 //   score 0 is sigmoid(z), score 1 the softmax over the n logits; the weights are the chosen scores as they are, or
-//   (renormalize) divided by their sum.  Equal scores: the lower index wins.  One warp per token.
+//   (renormalize) divided by their sum (+ norm_eps), and then times route_scale.  Equal scores: the lower index wins.
+//   With groups > 1 the experts stand in `groups` equal groups of neighbours; a group's mark is the sum of its two
+//   largest scores (its only score where a group is one expert), and only the experts of the `keep` groups with the
+//   largest marks (of equal marks the lower group) can be chosen.  One warp per token.
 //   Writes expert [T, top] int32, weight [T, top] float32 and gate [T] = sigmoid(z[n]).
 //
 // moe_sort_kernel: orders the T * top (token, choice) pairs by expert.  Writes start [n + 1] (the slots of expert e are
@@ -20,7 +23,9 @@ constexpr int MOE_MAX_PER_LANE = 16;      // up to 512 experts
 
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ z, int ld, int T, int n, int top, int score, int renormalize,
-                 int has_gate, int* __restrict__ expert, float* __restrict__ weight, float* __restrict__ gate) {
+                 int has_gate, int* __restrict__ expert, float* __restrict__ weight, float* __restrict__ gate,
+                 int groups, int keep, float route_scale, float norm_eps) {
+    __shared__ float held[4][32 * MOE_MAX_PER_LANE], marks[4][32 * MOE_MAX_PER_LANE];
     pdl_enter(TR_MOE_ROUTE);
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -52,6 +57,38 @@ moe_route_kernel(const float* __restrict__ z, int ld, int T, int n, int top, int
 #pragma unroll
     for (int c = 0; c < MOE_MAX_PER_LANE; ++c)
         if (lane + 32 * c >= n || !(s[c] == s[c])) s[c] = -1.f;      // outside, or not a number: never preferred
+    if (groups > 1) {
+        float* my = held[threadIdx.x >> 5];
+        float* mk = marks[threadIdx.x >> 5];
+        const int size = n / groups;
+#pragma unroll
+        for (int c = 0; c < MOE_MAX_PER_LANE; ++c)
+            if (lane + 32 * c < n) my[lane + 32 * c] = s[c];
+        __syncwarp();
+        for (int g = lane; g < groups; g += 32) {
+            float a = -1.f, b = -1.f;      // the group's two largest scores
+            for (int i = 0; i < size; ++i) {
+                const float v = my[g * size + i];
+                if (v > a) { b = a; a = v; }
+                else if (v > b) b = v;
+            }
+            mk[g] = size > 1 ? a + b : a;
+        }
+        __syncwarp();
+        // a group takes part if fewer than `keep` groups come before it (a larger mark, or an equal one and a lower
+        // index); the scores in `my` have been read, so the flags go there
+        for (int g = lane; g < groups; g += 32) {
+            int before = 0;
+            for (int o = 0; o < groups; ++o) before += (mk[o] > mk[g] || (mk[o] == mk[g] && o < g)) ? 1 : 0;
+            my[g] = before < keep ? 1.f : 0.f;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < MOE_MAX_PER_LANE; ++c) {
+            const int e = lane + 32 * c;
+            if (e < n && my[e / size] == 0.f) s[c] = -1.f;
+        }
+    }
     float total = 0.f;
     float mine = 0.f;      // lane j keeps the weight of choice j
     int mine_e = 0;
@@ -77,7 +114,7 @@ moe_route_kernel(const float* __restrict__ z, int ld, int T, int n, int top, int
         if (lane == (j & 31)) {
             if (j >= 32) {      // (more than 32 choices: written as they come)
                 expert[(size_t)t * top + j] = best_e;
-                weight[(size_t)t * top + j] = wj;
+                weight[(size_t)t * top + j] = wj * route_scale;
             } else {
                 mine = wj;
                 mine_e = best_e;
@@ -86,7 +123,7 @@ moe_route_kernel(const float* __restrict__ z, int ld, int T, int n, int top, int
     }
     if (lane < top && lane < 32) {
         expert[(size_t)t * top + lane] = mine_e;
-        weight[(size_t)t * top + lane] = renormalize ? mine / total : mine;
+        weight[(size_t)t * top + lane] = (renormalize ? mine / (total + norm_eps) : mine) * route_scale;
     }
     if (gate && lane == 0) gate[t] = has_gate ? 1.f / (1.f + expf(-row[n])) : 1.f;
 }
@@ -140,16 +177,17 @@ rows_by_index_kernel(const T* __restrict__ x, const int* __restrict__ index, int
     for (int i = threadIdx.x; i < E; i += blockDim.x) out[(size_t)s * E + i] = from_float<T>(to_float(src[i]) * m);
 }
 
-// planes_by_index_kernel: out[index[s] % div][index[s] / div][:] = rows[s][:] (out float32): the experts' outputs back
-// to one plane per choice, row = token.
+// planes_by_index_kernel: out[index[s] % div][index[s] / div][:] = rows[s][:] * scale[index[s]] (out float32; scale
+// may be absent): the experts' outputs back to one plane per choice, row = token.
 template <typename T>
 __global__ void __launch_bounds__(256)
 planes_by_index_kernel(const T* __restrict__ rows, const int* __restrict__ index, int div, size_t plane,
-                       float* __restrict__ out, int E) {
+                       const float* __restrict__ scale, float* __restrict__ out, int E) {
     pdl_enter(TR_MOE_SORT);
     const int s = blockIdx.x, p = index[s];
+    const float m = scale ? scale[p] : 1.f;
     float* dst = out + (size_t)(p % div) * plane + (size_t)(p / div) * E;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) dst[i] = to_float(rows[(size_t)s * E + i]);
+    for (int i = threadIdx.x; i < E; i += blockDim.x) dst[i] = to_float(rows[(size_t)s * E + i]) * m;
 }
 
 }  // namespace air
@@ -163,23 +201,25 @@ AIR_API int air_rows_by_index(const void* x, int dtype, const int* index, int di
     return 0;
 }
 
-AIR_API int air_planes_by_index(const void* rows, int dtype, const int* index, int div, long long plane, float* out,
-                                int n, int E, cudaStream_t stream) {
+AIR_API int air_planes_by_index(const void* rows, int dtype, const int* index, int div, long long plane,
+                                const float* scale, float* out, int n, int E, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (div <= 0) return AIR_ERR_BAD_ARGUMENT;
     AIR_DISPATCH(dtype, TT, return air::launch(air::planes_by_index_kernel<TT>, n, 256, 0, stream, (const TT*)rows, index,
-                                               div, (size_t)plane, out, E));
+                                               div, (size_t)plane, scale, out, E));
     return 0;
 }
 
 AIR_API int air_moe_route(const float* z, int ld, int T, int n, int top, int score, int renormalize, int has_gate,
-                          int* expert, float* weight, float* gate, cudaStream_t stream) {
+                          int* expert, float* weight, float* gate, int groups, int keep, float route_scale,
+                          float norm_eps, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (n <= 0 || n > 32 * air::MOE_MAX_PER_LANE || top <= 0 || top > n || top > 32 || ld < n + (has_gate ? 1 : 0) ||
         score < 0 || score > 1)
         return AIR_ERR_BAD_ARGUMENT;
+    if (groups > 1 && (n % groups || keep <= 0 || keep > groups || top > keep * (n / groups))) return AIR_ERR_BAD_ARGUMENT;
     return air::launch(air::moe_route_kernel, (T + 3) / 4, 128, 0, stream, z, ld, T, n, top, score, renormalize,
-                       has_gate, expert, weight, gate);
+                       has_gate, expert, weight, gate, groups, keep, route_scale, norm_eps);
 }
 
 AIR_API int air_moe_sort(const int* expert, int pairs, int n, int tile_rows, int* start, int* pair_of_slot, int* tiles,

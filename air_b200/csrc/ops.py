@@ -17,6 +17,11 @@ c_int, c_float, c_void_p, c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_vo
 
 _SIGNATURES = {
     "air_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    "air_bigram_embedding": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p,
+                             c_void_p],
+    "air_remember_tokens": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "air_stream_add": [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p],
     "air_add_parts": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p],
     "air_add_prenorm": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "air_logits_post": [c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p],
@@ -36,8 +41,8 @@ _SIGNATURES = {
                               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_void_p, c_void_p],
     "air_latent_prepare": [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                           c_void_p],
+                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                           c_void_p, c_void_p],
     "air_grouped_attention": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_int,
                               c_void_p],
@@ -45,13 +50,14 @@ _SIGNATURES = {
                         c_void_p, c_void_p],
     "air_masked_softmax": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                            c_void_p, c_void_p],
-    "air_moe_route": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "air_moe_route": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                      c_int, c_float, c_float, c_void_p],
     "air_moe_sort": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "air_grouped_gemm": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_longlong,
                          c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int,
-                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "air_rows_by_index": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
-    "air_planes_by_index": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p],
+    "air_planes_by_index": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "air_qkv_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                         c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_void_p, c_void_p],
@@ -62,6 +68,8 @@ _SIGNATURES = {
                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_float, c_void_p],
     "air_gated_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float,
                           c_void_p],
+    "air_polynorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float,
+                     c_float, c_void_p],
     "air_glu": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p],
     "air_scaled_norm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int,
                         c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
@@ -197,6 +205,55 @@ def embedding(table, ids, out, status=None, last_token=None, multiplier=1.0):
                                  out.data_ptr(), out.shape[0], E, V, float(multiplier), _ptr(status), _stream()),
            "embedding")
     return out
+
+
+def bigram_embedding(table, pairs, ids, positions, token_seq, previous, out, out2, resolved, buckets, mul_prev, mul_cur,
+                     status=None, last_token=None):
+    """out[t] = table[id] + pairs[(prev * mul_prev + id * mul_cur) % buckets] as float32 (pairs[buckets] at position
+    0); prev is the row above where it belongs to the same request, else previous[slot, 0].  out2: a second copy or
+    None.  resolved int32 [T] receives the ids used (an id -(s+1) is replaced by last_token[s])."""
+    V, E = table.shape
+    T = out.shape[0]
+    _req(table, "table", _FLOATS)
+    _req(pairs, "pairs", (table.dtype,), (buckets + 1, E))
+    for name, x in (("ids", ids), ("positions", positions), ("token_seq", token_seq), ("resolved", resolved)):
+        _req(x, name, _I32, (T,))
+    _req(previous, "previous", _I32)
+    _req(out, "out", (torch.float32,), (T, E))
+    if out2 is not None:
+        _req(out2, "out2", (torch.float32,), (T, E))
+    if last_token is not None:
+        _req(last_token, "last_token", _I32)
+    _check(_get("air_bigram_embedding")(table.data_ptr(), pairs.data_ptr(), _DT[table.dtype], ids.data_ptr(),
+                                        positions.data_ptr(), token_seq.data_ptr(), previous.data_ptr(),
+                                        _ptr(last_token), out.data_ptr(), _ptr(out2), resolved.data_ptr(), T, E, V,
+                                        int(buckets), int(mul_prev), int(mul_cur), _ptr(status), _stream()),
+           "bigram_embedding")
+    return out
+
+
+def remember_tokens(resolved, q_start, slots, previous, entries):
+    """previous[slots[e], 0] = resolved[q_start[e + 1] - 1] for every entry e of the step."""
+    _req(resolved, "resolved", _I32)
+    _req(q_start, "q_start", _I32)
+    _req(slots, "slots", _I32)
+    _req(previous, "previous", _I32)
+    if q_start.shape[0] < entries + 1 or slots.shape[0] < entries:
+        raise KernelError("remember_tokens: fewer entries than said")
+    _check(_get("air_remember_tokens")(resolved.data_ptr(), q_start.data_ptr(), slots.data_ptr(), previous.data_ptr(),
+                                       int(entries), _stream()), "remember_tokens")
+
+
+def stream_add(h, again=None, row=None):
+    """h += again + row: again float32 of h's shape or None, row float32 [E] (the same for every row of h) or None."""
+    E = h.shape[-1]
+    _req(h, "h", (torch.float32,), (None, E))
+    if again is not None:
+        _req(again, "again", (torch.float32,), tuple(h.shape))
+    if row is not None:
+        _req(row, "row", (torch.float32,), (E,))
+    _check(_get("air_stream_add")(h.data_ptr(), _ptr(again), _ptr(row), E, h.numel(), _stream()), "stream_add")
+    return h
 
 
 def add_parts(h, delta):
@@ -530,16 +587,21 @@ def qk_normed_prepare(proj, q_weight, k_weight, eps, freq, pairing, magnitude, p
 
 
 def latent_prepare(proj, c_weight, eps, freq, positions, token_seq, block_table, q_plain, q_full, cache, owns,
-                   status=None):
-    """From the first projection of a latent-attention layer (float32 [T, H (d + rot) (+ R + rot where owns)]) to
-    q_plain [T, H, d] (the cache's type), the rotated parts in q_full[:, :, R:] (float32 [T, H, R + rot]) and, where
-    owns, the row [rms(c) * c_weight | rotated kr] in the pages (cache [pages, P, R + rot])."""
+                   status=None, gate_out=None, gate_column=0):
+    """From the first projection of a latent-attention layer (float32 [T, H (d + rot) (+ R + rot where owns) (+ more)])
+    to q_plain [T, H, d] (the cache's type), the rotated parts in q_full[:, :, R:] (float32 [T, H, R + rot]) and, where
+    owns, the row [rms(c) * c_weight | rotated kr] in the pages (cache [pages, P, R + rot]).  freq None: nothing is
+    rotated (rot = 0).  gate_out float32 [T, H] = sigmoid of the H columns of proj from gate_column on."""
     T, H, d = q_plain.shape
     P, width = cache.shape[1], cache.shape[2]
     rot = 2 * freq.numel() if freq is not None else 0
     R = width - rot
-    ld = H * (d + rot) + (width if owns else 0)
-    _req(proj, "proj", (torch.float32,), (T, ld))
+    ld = proj.shape[1]
+    _req(proj, "proj", (torch.float32,), (T, None))
+    if ld < H * (d + rot) + (width if owns else 0):
+        raise KernelError(f"latent_prepare: proj has {ld} columns, too few")
+    if gate_out is not None:
+        _req(gate_out, "gate_out", (torch.float32,), (T, H))
     if freq is not None:
         _req(freq, "freq", (torch.float64,))
     if owns:
@@ -553,14 +615,17 @@ def latent_prepare(proj, c_weight, eps, freq, positions, token_seq, block_table,
     _check(_get("air_latent_prepare")(
         proj.data_ptr(), ld, _ptr(c_weight), float(eps), _ptr(freq), positions.data_ptr(), token_seq.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], q_plain.data_ptr(), q_full.data_ptr(), cache.data_ptr(),
-        _DT[q_plain.dtype], 1 if owns else 0, T, H, d, rot, R, P, _ptr(status), _stream()), "latent_prepare")
+        _DT[q_plain.dtype], 1 if owns else 0, T, H, d, rot, R, P, _ptr(gate_out), int(gate_column), _ptr(status),
+        _stream()), "latent_prepare")
 
 
 def moe_route(z, experts, top, expert_out, weight_out, gate_out=None, has_gate=False, score="sigmoid",
-              renormalize=False):
+              renormalize=False, groups=0, keep=0, route_scale=1.0, norm_eps=0.0):
     """z float32 [T, >= experts (+ 1)]: router logits.  expert_out int32 [T, top], weight_out float32 [T, top]: the
-    experts with the largest scores (sigmoid(z), or softmax(z)) and those scores (divided by their sum where
-    renormalize); gate_out float32 [T] = sigmoid(z[:, experts]) where has_gate, else 1."""
+    experts with the largest scores (sigmoid(z), or softmax(z)) and those scores (divided by their sum + norm_eps where
+    renormalize), times route_scale; gate_out float32 [T] = sigmoid(z[:, experts]) where has_gate, else 1.  groups > 1:
+    only the experts of the `keep` best of `groups` equal groups of neighbours can be chosen, a group's mark being the
+    sum of its two largest scores."""
     T = z.shape[0]
     _req(z, "z", (torch.float32,))
     _req(expert_out, "expert_out", _I32, (T, top))
@@ -571,7 +636,8 @@ def moe_route(z, experts, top, expert_out, weight_out, gate_out=None, has_gate=F
         raise KernelError(f"moe_route: score {score!r}")
     _check(_get("air_moe_route")(z.data_ptr(), z.shape[1], T, int(experts), int(top), 1 if score == "softmax" else 0,
                                  1 if renormalize else 0, 1 if has_gate else 0, expert_out.data_ptr(),
-                                 weight_out.data_ptr(), _ptr(gate_out), _stream()), "moe_route")
+                                 weight_out.data_ptr(), _ptr(gate_out), int(groups), int(keep), float(route_scale),
+                                 float(norm_eps), _stream()), "moe_route")
 
 
 GROUP_TILE = 64      # rows of a tile of the grouped product
@@ -594,10 +660,11 @@ def moe_sort(expert, experts, start, pair_of_slot, tiles, num_tiles):
 
 def grouped_gemm(a, w, out, n, k, *, lda, ldo, groups, a_group_stride=0, o_group_stride=0, a_index=None, a_div=1,
                  a_scale=None, a_local=False, o_index=None, o_div=1, o_part_stride=0, o_local=False, start=None,
-                 rows_per_group=0, tiles=None, num_tiles=None, silu_mul=False, gate_block=0):
+                 rows_per_group=0, tiles=None, num_tiles=None, silu_mul=False, gate_block=0, o_scale=None):
     """out rows = a rows @ w[g]^T for every group g (w [groups, n (2n with silu_mul), k]); see grouped_gemm.cu for how
     rows are found.  Strides in elements.  out is float32 or of a's type; with silu_mul out = silu(gate) * linear, the
-    rows of w[g] being blocks of gate_block gate rows and as many linear rows in turn (0: all gate rows first)."""
+    rows of w[g] being blocks of gate_block gate rows and as many linear rows in turn (0: all gate rows first).
+    o_scale float32 (with o_index): the row written for slot s is multiplied by o_scale[o_index[s]], in 32-bit."""
     _req(a, "a", _FLOATS)
     _req(w, "w", (a.dtype,), (groups, 2 * n if silu_mul else n, k))
     _req(out, "out", (torch.float32, a.dtype))
@@ -609,12 +676,14 @@ def grouped_gemm(a, w, out, n, k, *, lda, ldo, groups, a_group_stride=0, o_group
             _req(x, name, _I32)
     if a_scale is not None:
         _req(a_scale, "a_scale", (torch.float32,))
+    if o_scale is not None:
+        _req(o_scale, "o_scale", (torch.float32,))
     _check(_get("air_grouped_gemm")(
         a.data_ptr(), int(lda), int(a_group_stride), _ptr(a_index), int(a_div), 1 if a_local else 0, _ptr(a_scale),
         w.data_ptr(), w.shape[1] * w.shape[2], out.data_ptr(), int(ldo), int(o_group_stride), _ptr(o_index), int(o_div),
         int(o_part_stride), 1 if o_local else 0, 1 if out.dtype == torch.float32 else 0, _ptr(start),
         int(rows_per_group), _ptr(tiles), _ptr(num_tiles), tiles.shape[0] if tiles is not None else 0, int(groups),
-        int(n), int(k), _DT[a.dtype], 1 if silu_mul else 0, int(gate_block), _stream()), "grouped_gemm")
+        int(n), int(k), _DT[a.dtype], 1 if silu_mul else 0, int(gate_block), _ptr(o_scale), _stream()), "grouped_gemm")
     return out
 
 
@@ -630,14 +699,17 @@ def rows_by_index(x, index, div, scale, out):
     return out
 
 
-def planes_by_index(rows, index, div, out):
-    """out[index[s] % div, index[s] // div] = rows[s]; rows [n, E], out float32 [div, T, E]."""
+def planes_by_index(rows, index, div, out, scale=None):
+    """out[index[s] % div, index[s] // div] = rows[s] * scale[index[s]] (scale float32 or None); rows [n, E], out
+    float32 [div, T, E]."""
     n, E = rows.shape
     _req(rows, "rows", _FLOATS)
     _req(index, "index", _I32, (n,))
     _req(out, "out", (torch.float32,), (div, None, E))
+    if scale is not None:
+        _req(scale, "scale", (torch.float32,))
     _check(_get("air_planes_by_index")(rows.data_ptr(), _DT[rows.dtype], index.data_ptr(), int(div), out.shape[1] * E,
-                                       out.data_ptr(), n, E, _stream()), "planes_by_index")
+                                       _ptr(scale), out.data_ptr(), n, E, _stream()), "planes_by_index")
     return out
 
 
@@ -713,11 +785,11 @@ def short_conv_silu(x, weight, state, y, q_start, slots, max_tokens):
     return y
 
 
-SCAN_DELTA, SCAN_GLA = 0, 1
+SCAN_DELTA, SCAN_GLA, SCAN_HGRN = 0, 1, 2
 
 
 def linear_scan(mode, q, k, v, decay, state, out, q_start, slots, token_seq, q_scale=1.0, beta=None, a_log=None,
-                dt_bias=None, tau=1.0, unit=False, unit_eps=1e-6):
+                dt_bias=None, tau=1.0, unit=False, unit_eps=1e-6, lower=None, gate_bias=None):
     """A state S [d, dv] per head and request, updated token by token in 32-bit and read out after each update.
     q, k float32 [T, G * d], v [T, H * dv] (each may be a band of columns of a wider matrix); head h reads q/k head
     h // (H / G); state [slots, H, d, dv]; out [T, H, dv]; token_seq [T]: the slot of each row's request (negative:
@@ -727,16 +799,20 @@ def linear_scan(mode, q, k, v, decay, state, out, q_start, slots, token_seq, q_s
       with unit, q and k are first divided by sqrt(sum of squares + unit_eps), q then multiplied by q_scale;
       S = g S; u = b (v - S^T k); S += k u^T; o = S^T q.
     SCAN_GLA: decay [T, H * d] logits; alpha = sigmoid(decay)^(1 / tau); q is multiplied by q_scale;
-      S = diag(alpha) S + k v^T; o = S^T q."""
+      S = diag(alpha) S + k v^T; o = S^T q.
+    SCAN_HGRN: decay [T, H * d] logits, lower and gate_bias float32 [H * d]; alpha = lower + (1 - lower) *
+      sigmoid(decay + gate_bias); k is None (k = 1 - alpha); q = silu(q) * q_scale; the recurrence is SCAN_GLA's."""
     slots_n, H, d, dv = state.shape
     _req(state, "state", (torch.float32,))
     T = out.shape[0]
     _req(out, "out", (torch.float32,), (T, H, dv))
     qp, ldq = _columns(q, "q")
-    kp, ldk = _columns(k, "k")
+    kp, ldk = _columns(k, "k") if k is not None else (None, 0)
     vp, ldv = _columns(v, "v")
     dp, ldd = _columns(decay, "decay")
-    if q.shape[1] % d or k.shape != q.shape or v.shape[1] != H * dv:
+    if (k is None) != (mode == SCAN_HGRN):
+        raise KernelError("linear_scan: keys are given except where the gate makes them")
+    if q.shape[1] % d or (k is not None and k.shape != q.shape) or v.shape[1] != H * dv:
         raise KernelError("linear_scan: q, k or v do not fit the state's shape")
     G = q.shape[1] // d
     if G == 0 or H % G:
@@ -751,6 +827,11 @@ def linear_scan(mode, q, k, v, decay, state, out, q_start, slots, token_seq, q_s
     elif mode == SCAN_GLA:
         if decay.shape[1] != H * d or G != H:
             raise KernelError("linear_scan: gated linear attention takes a decay per key channel of every head")
+    elif mode == SCAN_HGRN:
+        if decay.shape[1] != H * d or G != H:
+            raise KernelError("linear_scan: a forget gate per key channel of every head")
+        a_log, dt_bias = _req(lower, "lower", (torch.float32,), (H * d,)), _req(gate_bias, "gate_bias",
+                                                                                   (torch.float32,), (H * d,))
     else:
         raise KernelError(f"linear_scan: mode {mode}")
     if d > 1024:
@@ -776,11 +857,11 @@ def linear_scan(mode, q, k, v, decay, state, out, q_start, slots, token_seq, q_s
 
 def gated_rmsnorm(o, gate, weight, eps, out, token_seq):
     """out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * weight * silu(gate[t, h, :]).  o float32 [T, H, dv]; gate
-    float32 [T, H * dv] (may be a band of columns); weight float32 [dv]; out [T, H * dv]."""
+    float32 [T, H * dv] (may be a band of columns) or None (no gate); weight float32 [dv]; out [T, H * dv]."""
     T, H, dv = o.shape
     _req(o, "o", (torch.float32,))
-    gp, ldg = _columns(gate, "gate")
-    if gate.shape != (T, H * dv):
+    gp, ldg = _columns(gate, "gate") if gate is not None else (None, 0)
+    if gate is not None and gate.shape != (T, H * dv):
         raise KernelError("gated_rmsnorm: the gate does not fit")
     _req(weight, "weight", (torch.float32,), (dv,))
     _req(out, "out", _FLOATS, (T, H * dv))
@@ -812,6 +893,23 @@ def glu(gate_up, out, block=None, alpha=1.0, limit=0.0, shift=0.0):
     _req(out, "out", _FLOATS)
     _check(_get("air_glu")(gate_up.data_ptr(), _DT[gate_up.dtype], out.data_ptr(), _DT[out.dtype], T, I, block,
                            float(alpha), float(limit), float(shift), _stream()), "glu")
+    return out
+
+
+def polynorm(z, bias, coefficients, eps, out, width):
+    """out[t, :width] = a N(u) + b N(u^2) + c N(u^3) + e with u = z[t] + bias, powers per element, N(x) = x /
+    sqrt(mean(x^2) + eps) over the row, (a, b, c, e) = coefficients; z float32 [T, width]; out [T, >= width] gets 1 in
+    column `width` (if it has one) and 0 behind it."""
+    T = z.shape[0]
+    zp, ld = _columns(z, "z")
+    if z.shape[1] != width:
+        raise KernelError("polynorm: z does not have `width` columns")
+    if bias is not None:
+        _req(bias, "bias", (torch.float32,), (width,))
+    _req(out, "out", _FLOATS, (T, None))
+    a, b, c, e = (float(v) for v in coefficients)
+    _check(_get("air_polynorm")(zp, ld, _ptr(bias), out.data_ptr(), _DT[out.dtype], out.shape[1], T, int(width), a, b,
+                                c, e, float(eps), _stream()), "polynorm")
     return out
 
 

@@ -9,11 +9,14 @@
 //   linear_scan_kernel       a state S [d, dv] per head, updated token by token, read out after each update:
 //                              DELTA  S = g S;  u = beta (v - S^T k);  S += k u^T;  o = S^T q   (one decay per head)
 //                              GLA    S = diag(alpha) S + k v^T;  o = S^T q                      (a decay per key channel)
+//                              HGRN   the same recurrence with k = 1 - alpha: the gate that forgets also says how
+//                                     much is written; alpha = l + (1 - l) sigmoid(z + bias) with a lower bound l per
+//                                     channel, q = silu(q)
 //                            Columns of S do not depend on one another, so a block takes a few of them and a column is
 //                            held in the registers of L lanes of one warp; the tokens of a portion are taken in order.
 //                            What a token's output is depends on the state and the tokens before it only, not on how
 //                            the request was cut into steps or on the rest of the batch.
-//   gated_rmsnorm_kernel     out[t, h, :] = o / sqrt(mean(o^2) + eps) * w * silu(gate[t, h, :])
+//   gated_rmsnorm_kernel     out[t, h, :] = o / sqrt(mean(o^2) + eps) * w * silu(gate[t, h, :]) (without a gate: * w)
 #include "common.cuh"
 
 namespace air {
@@ -81,7 +84,7 @@ short_conv_silu_kernel(const float* __restrict__ x, int ld, const float* __restr
     }
 }
 
-enum { SCAN_DELTA = 0, SCAN_GLA = 1 };
+enum { SCAN_DELTA = 0, SCAN_GLA = 1, SCAN_HGRN = 2 };
 constexpr int SCAN_THREADS = 128;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -100,13 +103,15 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 //                        delta rule, q's scale for gated linear attention), zeros from d to dpad
 //   dec                  DELTA [T, H, 2]: g = exp(-exp(a_log) softplus(decay + dt_bias)) and b = sigmoid(beta)
 //                        GLA   [T, H, dpad]: alpha = sigmoid(decay)^(1 / tau) per key channel, zeros from d on
+//                        HGRN  [T, H, dpad]: alpha = l + (1 - l) sigmoid(decay + bias); kq's k is 1 - alpha (no k is
+//                              read) and its q is silu(q) * q_scale
 struct ScanPrepArgs {
     const float* q; int ldq;         // [T, ldq]: head g's d elements at column g * d
     const float* k; int ldk;
     const float* decay; int ldd;     // DELTA: [T, ldd] one logit per head;  GLA: [T, ldd] d logits per head
     const float* beta; int ldb;      // DELTA: [T, ldb] one logit per head
-    const float* a_log;              // DELTA: [H]
-    const float* dt_bias;            // DELTA: [H]
+    const float* a_log;              // DELTA: [H];  HGRN: the lower bounds l [H * d]
+    const float* dt_bias;            // DELTA: [H];  HGRN: the gate's bias [H * d]
     const int* token_seq;
     float* kq;
     float* dec;
@@ -121,8 +126,26 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(const ScanPrepArgs p)
     pdl_enter(TR_SCAN);
     const int t = blockIdx.x, g = blockIdx.y;
     if (p.token_seq[t] < 0) return;
-    const float* kin = p.k + (size_t)t * p.ldk + g * p.d;
     const float* qin = p.q + (size_t)t * p.ldq + g * p.d;
+    if (MODE == SCAN_HGRN) {
+        const float* z = p.decay + (size_t)t * p.ldd + g * p.d;
+        float* out = p.kq + ((size_t)t * p.G + g) * 2 * p.dpad;
+        float* a = p.dec + ((size_t)t * p.H + g) * p.dpad;
+        for (int r = threadIdx.x; r < p.dpad; r += blockDim.x) {
+            float alpha = 0.f, k = 0.f, q = 0.f;
+            if (r < p.d) {
+                const float low = p.a_log[g * p.d + r];
+                alpha = low + (1.f - low) / (1.f + expf(-(z[r] + p.dt_bias[g * p.d + r])));
+                k = 1.f - alpha;
+                q = silu_f(qin[r]) * p.q_scale;
+            }
+            a[r] = alpha;
+            out[r] = k;
+            out[p.dpad + r] = q;
+        }
+        return;
+    }
+    const float* kin = p.k + (size_t)t * p.ldk + g * p.d;
     float kf = 1.f, qf = p.q_scale;
     if (p.unit) {
         float sk = 0.f, sq = 0.f;
@@ -286,7 +309,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
     }
 }
 
-// o [T, H, dv] float32; gate [T, ldg] float32 (head h at column h * dv); w [dv]; out [T, H * dv].
+// o [T, H, dv] float32; gate [T, ldg] float32 (head h at column h * dv) or null (no gate); w [dv]; out [T, H * dv].
 // One warp per (token, head).
 template <typename TO>
 __global__ void __launch_bounds__(128)
@@ -302,21 +325,22 @@ gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gate
     for (int i = lane; i < dv; i += 32) ss = fmaf(row[i], row[i], ss);
     ss = warp_sum(ss);
     const float scale = rsqrtf(ss / (float)dv + eps);
-    const float* gr = gate + (size_t)t * ldg + h * dv;
+    const float* gr = gate ? gate + (size_t)t * ldg + h * dv : nullptr;
     for (int i = lane; i < dv; i += 32)
-        out[(size_t)item * dv + i] = from_float<TO>(row[i] * scale * w[i] * silu_f(gr[i]));
+        out[(size_t)item * dv + i] = from_float<TO>(row[i] * scale * w[i] * (gr ? silu_f(gr[i]) : 1.f));
 }
 
 // rows of a column per lane: 16 up to 512 key channels, 32 beyond
 static int scan_rows(int d) { return d <= 512 ? 16 : 32; }
 
-template <int MODE>
+// PREP: what scan_prepare_kernel works out; MODE: the recurrence (HGRN's is GLA's)
+template <int PREP, int MODE = (PREP == SCAN_HGRN ? SCAN_GLA : PREP)>
 static int launch_scan(const ScanPrepArgs& prep, const ScanArgs& a, int T, int S, cudaStream_t stream) {
     const int R = scan_rows(a.d), L = a.L, dpad = L * R;
     if (L < 1 || L > 32 || (L & (L - 1)) || dpad < a.d || prep.dpad != dpad || (R == 32 && L != 32))
         return AIR_ERR_BAD_ARGUMENT;
     if (a.H > 65535 || S > 65535 || prep.G > 65535) return AIR_ERR_BAD_ARGUMENT;
-    int rc = launch(scan_prepare_kernel<MODE>, dim3(T, prep.G), 128, 0, stream, prep);
+    int rc = launch(scan_prepare_kernel<PREP>, dim3(T, prep.G), 128, 0, stream, prep);
     if (rc) return rc;
     ScanArgs p = a;
     const int CB = SCAN_THREADS / L;
@@ -379,7 +403,7 @@ AIR_API int air_short_conv_silu(const float* x, int ld, const float* w, float* s
                        slots, C, taps, chunk);
 }
 
-// kq: float32 workspace [T, G, 2, L * R] and dec: [T, H, 2] (mode 0) or [T, H, L * R] (mode 1), with R = 16 up to
+// kq: float32 workspace [T, G, 2, L * R] and dec: [T, H, 2] (mode 0) or [T, H, L * R] (modes 1, 2), with R = 16 up to
 // 512 key channels and 32 beyond, L the power of two with L * R >= d.
 AIR_API int air_linear_scan(int mode, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
                             const float* decay, int ldd, const float* beta, int ldb, const float* a_log,
@@ -399,6 +423,10 @@ AIR_API int air_linear_scan(int mode, const float* q, int ldq, const float* k, i
     a.H = H; a.G = G; a.d = d; a.dv = dv; a.L = L; a.tokens = 0;
     if (mode == air::SCAN_DELTA) return air::launch_scan<air::SCAN_DELTA>(pr, a, T, S, stream);
     if (mode == air::SCAN_GLA) return air::launch_scan<air::SCAN_GLA>(pr, a, T, S, stream);
+    if (mode == air::SCAN_HGRN) {
+        if (G != H || !a_log || !dt_bias) return AIR_ERR_BAD_ARGUMENT;
+        return air::launch_scan<air::SCAN_HGRN>(pr, a, T, S, stream);
+    }
     return AIR_ERR_BAD_ARGUMENT;
 }
 

@@ -11,9 +11,9 @@ import torch
 
 from ..csrc import ops
 from ..parts import registry
-from ..parts.base import Runtime
+from ..parts.base import Norm, Runtime
 from ..parts.linear import Linear
-from ..parts.spec import ModelSpec
+from ..parts.spec import ModelSpec, PartSpec
 from ..weights.loader import TensorSpec
 
 
@@ -23,11 +23,17 @@ class Model:
         self.spec = spec
         self.blocks = [registry.BLOCKS.get(b.kind)(b) for b in spec.layers]
         self.final_norm = registry.NORMS.get(spec.final_norm.kind)(spec.final_norm, spec.final_norm_prefix)
+        emb = spec.embedding or PartSpec("tokens", {"vocab": spec.vocab_size, "hidden": spec.hidden_size,
+                                                    "multiplier": spec.embedding_multiplier})
+        self.embedder = registry.EMBEDDINGS.get(emb.kind)(emb, spec.embedding_name)
+        # runs that add the embedding's output to the stream again need a second copy of it
+        self.embedding_copies = 2 if any(run.add_embedding for run in spec.order) else 1
 
     # ------------------------------------------------------------------ tensors
     def tensor_specs(self) -> List[TensorSpec]:
         s = self.spec
-        specs = [TensorSpec(s.embedding_name, (s.vocab_size, s.hidden_size))]
+        specs = list(self.embedder.tensor_specs())
+        specs += [TensorSpec(name, (rows, s.hidden_size), wide=True) for name, rows in s.stream_tables]
         for b in self.blocks:
             specs += b.tensor_specs()
         specs += self.final_norm.tensor_specs()
@@ -44,7 +50,9 @@ class Model:
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
-        self.embedding = tensors[self.spec.embedding_name]
+        self.embedder.load(tensors, rt)
+        self.embedding = self.embedder.table
+        self.stream_tables = {name: tensors[name].to(torch.float32).contiguous() for name, _ in self.spec.stream_tables}
         for b in self.blocks:
             b.load(tensors, rt)
         self.final_norm.load(tensors, rt)
@@ -53,6 +61,9 @@ class Model:
         bias = None if self.spec.output_bias_name is None else tensors[self.spec.output_bias_name]
         self.output_bias = None if bias is None else bias.to(torch.float32)
         self._planners = None
+        # for tests and for finding a fault layer by layer: a list that receives, after every run, a copy of the
+        # stream as it stands behind that run (what is still pending added to it)
+        self.tap = None
 
     def planners(self):
         """The parts that plan on the host, one for every plan key (Part.plan_key)."""
@@ -69,13 +80,14 @@ class Model:
     @property
     def graph_safe(self) -> bool:
         """Whether a decode step may be captured in a CUDA graph: no part reads the batch on the host."""
-        return all(b.graph_safe for b in self.blocks) and getattr(self.final_norm, "graph_safe", False)
+        return all(b.graph_safe for b in self.blocks) and getattr(self.final_norm, "graph_safe", False) \
+            and getattr(self.embedder, "graph_safe", False)
 
     def cache_needs(self):
         """Per run of the order list: the needs of the layer's mixer, or nothing for a run that
-        reads another run's cache."""
+        reads another run's cache; behind the runs, what the embedding keeps per request."""
         return [self.blocks[run.layer].cache_needs() if run.cache_from is None else ()
-                for run in self.spec.order]
+                for run in self.spec.order] + [tuple(self.embedder.cache_needs())]
 
     def weight_bytes(self) -> int:
         """Bytes of the tensors that one step reads (every weight once)."""
@@ -105,14 +117,20 @@ class Model:
         and returns float32 logits [wanted rows, vocab]."""
         rt = self.rt
         ctx.shared.clear()
-        h = torch.empty((ctx.num_tokens, self.spec.hidden_size), dtype=torch.float32, device=rt.device)
-        ops.embedding(self.embedding, ctx.token_ids, h, status=ctx.status, last_token=ctx.last_token,
-                      multiplier=self.spec.embedding_multiplier)
+        h, *again = self.embedder.forward(ctx, cache.views(len(self.spec.order)), self.embedding_copies)
         pending = None
         for i, run in enumerate(self.spec.order):
             owner = i if run.cache_from is None else run.cache_from
+            if run.add_embedding or run.add_row is not None:
+                # what the run adds to the stream ahead of its layer: the stream is completed first
+                Norm.add_delta(h, pending)
+                pending = None
+                row = None if run.add_row is None else self.stream_tables[run.add_row[0]][run.add_row[1]]
+                ops.stream_add(h, again[0] if run.add_embedding else None, row)
             h, pending = self.blocks[run.layer].forward(h, pending, ctx, cache.views(owner),
                                                         owns_cache=run.cache_from is None)
+            if self.tap is not None:
+                self.tap.append(Norm.add_delta(h.clone(), pending))
         R = ctx.logit_rows.shape[0]
         if R == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=rt.device)

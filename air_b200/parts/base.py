@@ -23,6 +23,8 @@ other parts of its block are.
   FeedForward       forward(x, ctx) -> as a mixer
   Block             forward(h, pending, ctx, cache, owns_cache) -> (h, pending): an arrangement of
                     parts around the residual stream; `pending` is a delta in the sense above
+  Embedding         forward(ctx, cache, copies) -> the stream's first rows from the step's token ids; may keep a
+                    state per request (cache_needs) like a mixer
 """
 from __future__ import annotations
 
@@ -301,6 +303,20 @@ class PositionEncoding(Part):
         """float32 [rotary_dim / 2]: the angle of pair i at position p is p * frequencies[i], for mixers whose
         kernels evaluate the angles themselves instead of reading a table (no bound on the position)."""
         return None
+
+
+class Embedding(Part):
+    """From token ids to rows of the stream.  forward(ctx, cache, copies) -> `copies` float32 tensors [T, hidden]
+    with the same contents (the stream itself, and one more where later runs add the embedding's output again);
+    `cache` holds the views of cache_needs(), as a mixer's does.  `table` is the token table [vocab, hidden], which a
+    model with a tied output matrix reads again at the end."""
+    table: Optional[torch.Tensor] = None
+
+    def cache_needs(self) -> Tuple[CacheNeed, ...]:
+        return ()
+
+    def forward(self, ctx, cache, copies: int = 1):
+        raise NotImplementedError
 
 
 class Mixer(Part):

@@ -39,28 +39,47 @@ class Block:
 
 @register_block("pre_norm")
 class PreNormBlock(Block):
-    """h = h + mixer(norm1(h)); h = h + feed_forward(norm2(h))
-    (AIR: src/reference/reference_executor.cpp:343-413).
-    Roles: mixer_norm, mixer, feed_forward_norm, feed_forward.
+    """h = h + m mixer(norm1(h)); h = h + m feed_forward(norm2(h)), m = 1 unless the block's parameter
+    residual_scale says otherwise (AIR: src/reference/reference_executor.cpp:343-413).
+    Roles: mixer_norm, mixer, and feed_forward_norm with feed_forward (a layer may lack these two).
 
     The residual stream h is float32.  Each addition is fused into the norm that follows
     it: the block receives the previous block's output still pending, and hands its own
     feed-forward output on in the same way; the model's final norm adds the last one.  A part may
     instead add its output into the stream itself (StepContext.residual) and return None: with
     many rows the library's product does that addition in its epilogue, in 32-bit, and the norm
-    that follows reads the stream alone."""
+    that follows reads the stream alone.  With m != 1 the parts return their outputs and the block hands them on
+    as a ScaledSum whose scale is m in every column, so the same kernel completes the stream and normalises.
+    The parameter idle lists (what follows the prefix, shape) of tensors that a model file may hold for the layer
+    although the layer does not use them (the second norm of a layer without feed-forward)."""
 
     def __init__(self, spec: BlockSpec):
         super().__init__(spec)
         self.mixer_norm = NORMS.get(spec.part("mixer_norm").kind)(spec.part("mixer_norm"), spec.name("mixer_norm"))
         self.mixer = MIXERS.get(spec.part("mixer").kind)(spec.part("mixer"), spec.name("mixer"))
-        self.ff_norm = NORMS.get(spec.part("feed_forward_norm").kind)(spec.part("feed_forward_norm"),
-                                                                      spec.name("feed_forward_norm"))
-        self.feed_forward = FEED_FORWARDS.get(spec.part("feed_forward").kind)(spec.part("feed_forward"),
-                                                                              spec.name("feed_forward"))
+        self.ff_norm = self.feed_forward = None
+        if "feed_forward" in spec.parts:
+            self.ff_norm = NORMS.get(spec.part("feed_forward_norm").kind)(spec.part("feed_forward_norm"),
+                                                                          spec.name("feed_forward_norm"))
+            self.feed_forward = FEED_FORWARDS.get(spec.part("feed_forward").kind)(spec.part("feed_forward"),
+                                                                                  spec.name("feed_forward"))
+        self.residual_scale = float(spec.params.get("residual_scale", 1.0))
+        self.scale = None
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward)
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward) if p is not None)
+
+    def tensor_specs(self):
+        from ..weights.loader import TensorSpec
+        return super().tensor_specs() + [TensorSpec(self.spec.prefix + name, tuple(shape), optional=True, wide=True)
+                                         for name, shape in self.spec.params.get("idle", ())]
+
+    def load(self, tensors, rt):
+        super().load(tensors, rt)
+        if self.residual_scale != 1.0:
+            import torch
+            self.scale = torch.full((self.spec.part("mixer_norm")["size"],), self.residual_scale, dtype=torch.float32,
+                                    device=rt.device)
 
     def cache_needs(self):
         return self.mixer.cache_needs()
@@ -73,12 +92,33 @@ class PreNormBlock(Block):
             return norm.forward_prenormed(h, delta)
         return norm.forward(h, delta)
 
+    def _scaled(self, delta):
+        """What a part returned, as the sum that the next norm adds: m times it."""
+        if self.scale is None or delta is None:
+            return delta
+        import torch
+        from ..csrc import ops
+        from .base import GatedSum, ScaledSum
+
+        def f32(t):
+            return t if t.dtype == torch.float32 else ops.convert(t, torch.empty(t.shape, dtype=torch.float32,
+                                                                                  device=t.device))
+        if isinstance(delta, GatedSum):
+            if delta.gate is not None:
+                raise ops.KernelError("pre_norm with a residual scale: a gate per row is not offered")
+            return ScaledSum([(f32(t), self.scale) for t in (delta.a, delta.b) if t is not None])
+        if isinstance(delta, ScaledSum):
+            raise ops.KernelError("pre_norm with a residual scale: the part's output is scaled already")
+        return ScaledSum([(f32(delta), self.scale)])
+
     def forward(self, h, pending, ctx, cache, owns_cache=True):
-        ctx.residual = h
+        ctx.residual = h if self.scale is None else None     # scaled outputs are returned, not added by the parts
         x = self._norm(self.mixer_norm, h, pending, self.mixer, ctx, owns_cache)
-        a = self.mixer.forward(x, ctx, cache, owns_cache)      # None: the mixer has added its output to h itself
+        a = self._scaled(self.mixer.forward(x, ctx, cache, owns_cache))   # None: the mixer has added its output to h
+        if self.feed_forward is None:
+            return h, a
         x = self._norm(self.ff_norm, h, a, self.feed_forward, ctx)
-        return h, self.feed_forward.forward(x, ctx)
+        return h, self._scaled(self.feed_forward.forward(x, ctx))
 
 
 @register_block("parallel")

@@ -24,13 +24,17 @@ class RoutedExperts(FeedForward):
     """y = sum over the token's `top` experts e of expert_e(s_e x)  +  g shared(x).
 
     Router: z = Wr x in 32-bit; scores s = sigmoid(z) (score "sigmoid") or softmax(z); the `top` largest are chosen
-    (of equal scores the lower index); the weights are the chosen scores, divided by their sum where renormalize.  The
-    weight multiplies the expert's INPUT (the scaled row is rounded to the compute dtype like any input of a product),
-    which is not the same as weighting its output, since an expert is not linear.  expert(u) = Wdown (silu(Wgate u) *
+    (of equal scores the lower index); the weights are the chosen scores, divided by their sum (+ norm_eps) where
+    renormalize, times route_scale.  With groups = (count, keep) the experts stand in `count` equal groups of
+    neighbours, a group's mark is the sum of its two largest scores, and only experts of the `keep` groups with the
+    largest marks can be chosen.  With weight_on "input" (the default) the weight multiplies the expert's INPUT (the
+    scaled row is rounded to the compute dtype like any input of a product), which is not the same as weighting its
+    output, since an expert is not linear; with "output" it multiplies the expert's output, in 32-bit.  expert(u) = Wdown (silu(Wgate u) *
     (Wup u)).  The shared expert (shared_intermediate > 0) has the same form and runs for every token; with shared_gate
     its output is multiplied by g = sigmoid(w_sg . x), one number per token, else g = 1.
 
-    params: hidden, experts, top, intermediate, shared_intermediate, shared_gate, score, renormalize.
+    params: hidden, experts, top, intermediate, shared_intermediate, shared_gate, score, renormalize, norm_eps,
+    route_scale, groups, weight_on.
     Tensors: <prefix>router [experts, hidden], e<i>.gate, e<i>.up [intermediate, hidden], e<i>.down [hidden,
     intermediate], shared.gate, shared.up, shared.down, shared.sg [1, hidden].
 
@@ -52,6 +56,15 @@ class RoutedExperts(FeedForward):
         self.inter, self.shared_inter = p["intermediate"], int(p.get("shared_intermediate") or 0)
         self.shared_gate = bool(p.get("shared_gate", False)) and self.shared_inter > 0
         self.score, self.renormalize = p.get("score", "sigmoid"), bool(p.get("renormalize", False))
+        self.norm_eps, self.route_scale = float(p.get("norm_eps", 0.0)), float(p.get("route_scale", 1.0))
+        self.groups, self.keep = tuple(p["groups"]) if p.get("groups") else (0, 0)
+        self.weight_on = p.get("weight_on", "input")
+        if self.weight_on not in ("input", "output"):
+            raise ConfigError("data_error", f"routed experts: weight_on {self.weight_on!r} (input or output)")
+        if self.groups > 1 and (self.experts % self.groups or not (0 < self.keep <= self.groups)
+                                or self.top > self.keep * (self.experts // self.groups)):
+            raise ConfigError("data_error", "routed experts: the groups must be equal, keep between 1 and their number, "
+                                            "and the kept groups must hold at least `top` experts")
         if self.experts > 512 or self.top > 32:
             raise ConfigError("unsupported", "routed experts: up to 512 experts and 32 choices per token")
         self.shared = None
@@ -111,7 +124,9 @@ class RoutedExperts(FeedForward):
         weight = torch.empty((T, top), dtype=torch.float32, device=dev)
         gate = torch.empty((T,), dtype=torch.float32, device=dev) if self.shared_gate else None
         ops.moe_route(z, n, top, expert, weight, gate, has_gate=self.shared_gate, score=self.score,
-                      renormalize=self.renormalize)
+                      renormalize=self.renormalize, groups=self.groups, keep=self.keep, route_scale=self.route_scale,
+                      norm_eps=self.norm_eps)
+        on_input = self.weight_on == "input"
         pairs = T * top
         ints = torch.empty(n + 1 + pairs + 2 * (pairs // ops.GROUP_TILE + n) + 1, dtype=torch.int32, device=dev)
         start, pair_of_slot = ints[:n + 1], ints[n + 1:n + 1 + pairs]
@@ -123,10 +138,11 @@ class RoutedExperts(FeedForward):
         else:
             act = torch.empty((pairs, F), dtype=x.dtype, device=dev)
             ops.grouped_gemm(x, self.gate_up, act, F, E, lda=E, ldo=F, groups=n, a_index=pair_of_slot, a_div=top,
-                             a_scale=weight.view(-1), start=start, tiles=tiles, num_tiles=num_tiles, silu_mul=True,
-                             gate_block=self.block)
+                             a_scale=weight.view(-1) if on_input else None, start=start, tiles=tiles,
+                             num_tiles=num_tiles, silu_mul=True, gate_block=self.block)
             ops.grouped_gemm(act, self.down, y, E, F, lda=F, ldo=E, groups=n, o_index=pair_of_slot, o_div=top,
-                             o_part_stride=T * E, start=start, tiles=tiles, num_tiles=num_tiles)
+                             o_part_stride=T * E, start=start, tiles=tiles, num_tiles=num_tiles,
+                             o_scale=None if on_input else weight.view(-1))
         if self.shared is None:
             return y
         return GatedSum(y, self.shared.forward(x, ctx), gate)
@@ -137,8 +153,11 @@ class RoutedExperts(FeedForward):
         activation kernel, the grouped product for down, the results back to the planes."""
         top, (T, E) = self.top, x.shape
         pairs = T * top
-        rows = ops.rows_by_index(x, pair_of_slot, top, weight.view(-1), torch.empty((pairs, E), dtype=x.dtype, device=x.device))
+        on_input = self.weight_on == "input"
+        rows = ops.rows_by_index(x, pair_of_slot, top, weight.view(-1) if on_input else None,
+                                 torch.empty((pairs, E), dtype=x.dtype, device=x.device))
         ends = start[1:].clone()
         act = torch.empty((pairs, self.inter), dtype=x.dtype, device=x.device)
         ops.silu_mul(torch._grouped_mm(rows, self.gate_up.transpose(1, 2), offs=ends), act, block=self.block)
-        ops.planes_by_index(torch._grouped_mm(act, self.down.transpose(1, 2), offs=ends), pair_of_slot, top, y)
+        ops.planes_by_index(torch._grouped_mm(act, self.down.transpose(1, 2), offs=ends), pair_of_slot, top, y,
+                            scale=None if on_input else weight.view(-1))

@@ -124,3 +124,44 @@ class ClampedGLU(SwiGLU):
             act = torch.empty((x.shape[0], self.intermediate), dtype=self.rt.dtype, device=x.device)
             ops.glu(gu, act, block=self.block, alpha=shape[0], limit=shape[1], shift=shape[2])
         return self.down.f32_sums(act)
+
+
+@register_feed_forward("polynorm_mlp")
+class PolyNormMLP(FeedForward):
+    """down(act(up(x) + b_up)) + b_down with act = PolyNorm: a N(z) + b N(z^2) + c N(z^3) + e, where the powers are
+    taken element by element, N(u) = u / sqrt(mean(u^2) + eps) over a token's `intermediate` values, and (a, b, c, e)
+    are four learned numbers.  params: hidden, intermediate, eps.  Tensors: <prefix>up [intermediate, hidden], up.b
+    [intermediate], down [hidden, intermediate], down.b [hidden], act [4].
+
+    z leaves the first product in 32-bit; one kernel adds b_up, takes the three norms and writes the activation in the
+    compute dtype.  b_down rides in the second product: the matrix gets one more column that holds it (and zeros up
+    to a multiple of 8 columns), the activation a matching column of ones."""
+
+    graph_safe = True
+
+    def tensor_specs(self):
+        e, f, p = self.spec["hidden"], self.spec["intermediate"], self.prefix
+        return [TensorSpec(p + "up", (f, e)), TensorSpec(p + "up.b", (f,), wide=True), TensorSpec(p + "down", (e, f)),
+                TensorSpec(p + "down.b", (e,), wide=True),
+                TensorSpec(p + "act", (4,), init="one_plus_normal", std=0.3, wide=True)]
+
+    def load(self, tensors, rt):
+        super().load(tensors, rt)
+        p = self.prefix
+        self.intermediate, self.eps = self.spec["intermediate"], float(self.spec["eps"])
+        self.up = Linear(tensors[p + "up"], rt.status)
+        self.up_bias = tensors[p + "up.b"].to(torch.float32).contiguous()
+        down = tensors[p + "down"]
+        f = self.intermediate
+        self.padded = (f // 8 + 1) * 8
+        w = torch.zeros((down.shape[0], self.padded), dtype=down.dtype, device=down.device)
+        w[:, :f] = down
+        w[:, f] = tensors[p + "down.b"].to(down.dtype)
+        self.down = Linear(w, rt.status)
+        self.coefficients = tuple(float(v) for v in tensors[p + "act"].to(torch.float32).cpu().tolist())
+
+    def forward(self, x, ctx):
+        z = self.up.f32(x)
+        act = torch.empty((x.shape[0], self.padded), dtype=self.rt.dtype, device=x.device)
+        ops.polynorm(z, self.up_bias, self.coefficients, self.eps, act, self.intermediate)
+        return self.down.f32_sums(act)

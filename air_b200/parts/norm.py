@@ -51,6 +51,21 @@ class RMSNorm(Norm):
         return PreNormed(xg, ss, self.eps)
 
 
+@register_norm("rms_scalar")
+class ScalarRMSNorm(RMSNorm):
+    """x * rsqrt(mean(x^2) + eps) * g with ONE learned number g for all columns.  params: size, eps; tensor as for
+    "rms".  Tensor: <prefix><tensor> [] (a scalar).  The kernels are RMSNorm's: g is spread over a vector at load."""
+
+    def tensor_specs(self):
+        return [TensorSpec(self.prefix + self.spec.get("tensor", "weight"), (), init="one_plus_normal", wide=True)]
+
+    def load(self, tensors, rt):
+        Norm.load(self, tensors, rt)
+        g = tensors[self.prefix + self.spec.get("tensor", "weight")]
+        self.weight = g.reshape(1).expand(self.spec["size"]).contiguous()
+        self.eps = float(self.spec["eps"])
+
+
 @register_norm("rms_after")
 class PostRMSNorm(Norm):
     """The norm of a layer that normalises after the sum: the stream itself becomes rms(alpha * h + delta) * w, with

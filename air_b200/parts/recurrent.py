@@ -166,3 +166,56 @@ class GatedLinearAttention(_StateMixer):
         ops.linear_scan(ops.SCAN_GLA, self._band(proj, "q"), self._band(proj, "k"), self._band(proj, "v"), z,
                         state.state, o, ctx.q_start, ctx.slots, ctx.token_seq, q_scale=d ** -0.5, tau=self.tau)
         return self._finish(o, proj, ctx)
+
+
+@register_mixer("hgrn2")
+class HGRN2(_StateMixer):
+    """Gated linear attention whose forget gate also decides what is written (HGRN2).  q = silu(W_q x) (heads x
+    head_dim), v = W_v x (heads x v_dim); per head and channel f = l + (1 - l) sigmoid(W_f x + b_f) with a learned lower
+    bound l; per head and token
+
+        S = diag(f) S + (1 - f) v^T;   o = S^T q
+
+    (no key, no other scale), then o / sqrt(mean(o^2) + eps) * norm over each head's v_dim numbers (one weight for all
+    heads, no gate) and the output projection.  S is the request's state, 32-bit, zero at its start.  The gate, its
+    sigmoid and 1 - f are 32-bit; the recurrence is gated linear attention's with k = 1 - f.
+
+    params: hidden, heads, head_dim, v_dim, eps.  Tensors: <prefix>q, f [heads*head_dim, hidden]; f.b, lower
+    [heads*head_dim]; v [heads*v_dim, hidden]; norm [v_dim]; o [hidden, heads*v_dim]."""
+
+    def __init__(self, spec, prefix=""):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden, self.heads, self.head_dim, self.v_dim = p["hidden"], p["heads"], p["head_dim"], p["v_dim"]
+        self.eps = float(p["eps"])
+        if self.head_dim > 1024:
+            raise ConfigError("unsupported", f"hgrn2: {self.head_dim} channels per head (up to 1,024)")
+
+    def cache_needs(self):
+        return (SlotState((self.heads, self.head_dim, self.v_dim)),)
+
+    def tensor_specs(self):
+        p, e, H, d, dv = self.prefix, self.hidden, self.heads, self.head_dim, self.v_dim
+        return [TensorSpec(p + "q", (H * d, e)), TensorSpec(p + "f", (H * d, e)), TensorSpec(p + "f.b", (H * d,), wide=True),
+                TensorSpec(p + "lower", (H * d,), init="uniform", std=0.9, wide=True), TensorSpec(p + "v", (H * dv, e)),
+                TensorSpec(p + "norm", (dv,), init="one_plus_normal", wide=True), TensorSpec(p + "o", (e, H * dv))]
+
+    def load(self, tensors, rt):
+        super().load(tensors, rt)
+        p = self.prefix
+        self._project(tensors, ["q", "f", "v"], rt)
+        f32 = lambda n: tensors[p + n].to(torch.float32).contiguous()
+        self.gate_bias, self.lower, self.norm_weight = f32("f.b"), f32("lower"), f32("norm")
+        self.o = Linear(tensors[p + "o"], rt.status)
+
+    def forward(self, x, ctx, cache, owns_cache=True):
+        (state,) = cache
+        T, H, dv = x.shape[0], self.heads, self.v_dim
+        proj = self.proj.f32(x)
+        o = torch.empty((T, H, dv), dtype=torch.float32, device=x.device)
+        ops.linear_scan(ops.SCAN_HGRN, self._band(proj, "q"), None, self._band(proj, "v"), self._band(proj, "f"),
+                        state.state, o, ctx.q_start, ctx.slots, ctx.token_seq, lower=self.lower,
+                        gate_bias=self.gate_bias)
+        y = torch.empty((T, H * dv), dtype=self.rt.dtype, device=o.device)
+        ops.gated_rmsnorm(o, None, self.norm_weight, self.eps, y, ctx.token_seq)
+        return self.o.f32_sums(y)

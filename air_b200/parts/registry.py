@@ -38,6 +38,7 @@ FEED_FORWARDS = _Registry("feed-forward")
 NORMS = _Registry("norm")
 POSITION_ENCODINGS = _Registry("position encoding")
 BLOCKS = _Registry("block arrangement")
+EMBEDDINGS = _Registry("embedding")
 
 
 def register_mixer(kind, cls=None):
@@ -58,6 +59,10 @@ def register_position_encoding(kind, cls=None):
 
 def register_block(kind, cls=None):
     return BLOCKS.register(kind, cls)
+
+
+def register_embedding(kind, cls=None):
+    return EMBEDDINGS.register(kind, cls)
 
 
 class Architecture(NamedTuple):

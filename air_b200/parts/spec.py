@@ -37,6 +37,8 @@ class BlockSpec:
     prefix: str
     parts: Mapping[str, PartSpec]
     names: Mapping[str, str] = field(default_factory=dict)
+    params: Mapping[str, Any] = field(default_factory=dict)    # constants of the arrangement itself (a multiplier
+                                                               # on what the sub-layers add to the stream, say)
 
     def part(self, role: str) -> PartSpec:
         try:
@@ -53,9 +55,17 @@ class BlockSpec:
 @dataclass(frozen=True)
 class RunStep:
     """One run of a layer.  cache_from: None for a run that keeps a cache of its own, else
-    the index (in the order list) of the earlier run whose cache this run reads."""
+    the index (in the order list) of the earlier run whose cache this run reads.
+
+    What the stream receives right before the run, after everything that earlier runs left pending has been
+    added: add_embedding, the embedding's output of this step once more (x += x0); add_row = (name, r), row r of
+    the model's table `name` (ModelSpec.stream_tables), the same vector for every token.  A stretch of layers that
+    runs several times over with the same weights is written as its runs, one after the other, each with a cache
+    of its own, and the first run of each pass carries what the pass adds."""
     layer: int
     cache_from: Optional[int] = None
+    add_embedding: bool = False
+    add_row: Optional[Tuple[str, int]] = None
 
 
 @dataclass(frozen=True)
@@ -76,6 +86,11 @@ class ModelSpec:
     output_bias_name: Optional[str] = None   # a float32 [vocab] tensor added to the logits
     logit_scale: float = 1.0                 # logits = (x W^T + bias) * logit_scale
     logit_softcap: float = 0.0               # > 0: logits = cap * tanh(logits / cap), after the scale
+    # How token ids become rows of the stream: None is the plain table `embedding_name` times
+    # embedding_multiplier; else a registered embedding (air_b200.parts.embedding), which may keep a state per request.
+    embedding: Optional[PartSpec] = None
+    # (name, rows): tables [rows, hidden] whose rows runs add to the stream (RunStep.add_row)
+    stream_tables: Tuple[Tuple[str, int], ...] = ()
 
     def validate(self) -> None:
         for i, run in enumerate(self.order):
@@ -86,3 +101,8 @@ class ModelSpec:
                     raise ValueError(f"order[{i}] reads the cache of run {run.cache_from}, which is not earlier")
                 if self.order[run.cache_from].cache_from is not None:
                     raise ValueError(f"order[{i}] reads the cache of run {run.cache_from}, which has none of its own")
+            if run.add_row is not None:
+                rows = dict(self.stream_tables).get(run.add_row[0])
+                if rows is None or not (0 <= run.add_row[1] < rows):
+                    raise ValueError(f"order[{i}] adds row {run.add_row[1]} of '{run.add_row[0]}', which the model "
+                                     f"does not have")

@@ -35,7 +35,7 @@ class TensorSpec:
     name: str
     shape: Tuple[int, ...]
     optional: bool = False
-    init: str = "normal"        # "normal": N(0, std);  "one_plus_normal": 1 + N(0, std);  "zeros"
+    init: str = "normal"        # "normal": N(0, std);  "one_plus_normal": 1 + N(0, std);  "zeros";  "uniform": U(0, std)
     std: float = 0.02
     integer: bool = False
     wide: bool = False          # the part computes with this tensor in 32 bits: stored in 32 bits it stays so
@@ -176,6 +176,8 @@ def random_tensors(specs: Sequence[TensorSpec], seed: int, dtype: torch.dtype, d
             continue
         if s.init == "zeros":
             t = torch.zeros(s.shape, dtype=torch.float32, device=device)
+        elif s.init == "uniform":
+            t = torch.empty(s.shape, dtype=torch.float32, device=device).uniform_(0.0, s.std, generator=g)
         else:
             t = torch.empty(s.shape, dtype=torch.float32, device=device).normal_(0.0, s.std, generator=g)
             if s.init == "one_plus_normal":
