@@ -29,9 +29,23 @@ class RMSNorm(Norm):
 
     prenorm = True      # x * scale(row) * w: forward_prenormed writes bfloat16(x * w) and leaves the scale to the consumer
 
+    @staticmethod
+    def _as_terms(delta):
+        """A sum of two branches without a gate is a sum of two terms without scales (float32 each)."""
+        if isinstance(delta, GatedSum) and delta.gate is None and \
+                all(t is None or t.dtype == torch.float32 for t in (delta.a, delta.b)):
+            return ScaledSum([(t, None) for t in (delta.a, delta.b) if t is not None])
+        return delta
+
     def forward(self, h, delta, rows=None):
         n = h.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, h.shape[1]), dtype=self.rt.dtype, device=h.device)
+        delta = self._as_terms(delta)
+        if isinstance(delta, GatedSum):
+            if rows is not None:
+                raise ops.KernelError("rms: a sum with a gate per row for chosen rows is not offered")
+            self.add_delta(h, delta)
+            delta = None
         if isinstance(delta, ScaledSum):
             # the outputs of sub-layers that stand side by side, each with its scale per column: one kernel
             # completes the stream with them and normalises
@@ -42,7 +56,7 @@ class RMSNorm(Norm):
         """As forward() without rows, for a part that takes its input as PreNormed: the stream is completed and
         the rows are written short of their scale, by many small blocks that do not wait for one another."""
         T, E = h.shape
-        if isinstance(delta, ScaledSum):
+        if isinstance(delta, (ScaledSum, GatedSum)):
             self.add_delta(h, delta)
             delta = None
         xg = torch.empty((T, E), dtype=torch.bfloat16, device=h.device)

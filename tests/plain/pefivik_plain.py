@@ -96,7 +96,7 @@ def run_order(n_layers, loop):
     return runs
 
 
-def latent_attention(h, w, p, eps, tap=None):
+def latent_attention(h, w, p, eps):
     """h [T, E] -> [T, E].  w: the layer's tensors by what follows 'mix.'."""
     T = h.shape[0]
     H, d, dv = p["heads"], p["dim"], p["vdim"]
@@ -113,8 +113,6 @@ def latent_attention(h, w, p, eps, tap=None):
         top = np.maximum(s.max(axis=1, keepdims=True), w["sink"][hd])
         e = np.exp(s - top)
         weights = e / (e.sum(axis=1, keepdims=True) + np.exp(w["sink"][hd] - top))
-        if tap is not None:
-            tap.setdefault("weights", []).append(weights)
         out[:, hd] = (weights @ v[:, hd]) * gate[:, hd:hd + 1]
     return out.reshape(T, H * dv) @ w["o"].T
 
@@ -151,8 +149,10 @@ def gated_expert(h, gate, up, down):
     return (silu(h @ gate.T) * (h @ up.T)) @ down.T
 
 
-def route(scores, top, count, keep):
-    """scores [n] -> the indices of the chosen experts, in falling order of score (of equal ones the lower index)."""
+def route(scores, top, count, keep, margins=None):
+    """scores [n] -> the indices of the chosen experts, in falling order of score (of equal ones the lower index).
+    margins (a list) receives by how much the choice was made: the smallest gap between a group that takes part and
+    one that does not, and between a chosen expert and one that could have been chosen."""
     n = scores.shape[0]
     size = n // count
     marks = []
@@ -164,25 +164,27 @@ def route(scores, top, count, keep):
     for g in order[:keep]:
         allowed[g * size:(g + 1) * size] = True
     cand = sorted((i for i in range(n) if allowed[i]), key=lambda i: (-scores[i], i))
+    if margins is not None:
+        if keep < count:
+            margins.append(float(marks[order[keep - 1]] - marks[order[keep]]))
+        if top < len(cand):
+            margins.append(float(scores[cand[top - 1]] - scores[cand[top]]))
     return cand[:top]
 
 
-def moe_ff(h, w, p, tap=None):
+def moe_ff(h, w, p, margins=None):
     """w: the layer's tensors by what follows 'mlp.'."""
     r = p["router"]
-    n, top = r["experts"], r["top"]
+    top = r["top"]
+    groups = r.get("groups") or {"count": 1, "keep": 1}
     s = sigmoid(h @ w["router"].T)
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
-        chosen = route(s[t], top, r["groups"]["count"], r["groups"]["keep"])
+        chosen = route(s[t], top, groups["count"], groups["keep"], margins)
         total = sum(s[t, e] for e in chosen) + 1e-20
-        if tap is not None:
-            rest = [s[t, e] for e in range(n) if e not in chosen]
-            tap.setdefault("margin", []).append(min(s[t, e] for e in chosen) - max(rest) if rest else 1.0)
-            tap.setdefault("chosen", []).append(chosen)
         for e in chosen:
-            out[t] += s[t, e] / total * r["scale"] * gated_expert(h[t:t + 1], w[f"e{e}.gate"], w[f"e{e}.up"],
-                                                                  w[f"e{e}.down"])[0]
+            out[t] += s[t, e] / total * r.get("scale", 1.0) * gated_expert(h[t:t + 1], w[f"e{e}.gate"], w[f"e{e}.up"],
+                                                                            w[f"e{e}.down"])[0]
     if p.get("shared"):
         out += gated_expert(h, w["shared.gate"], w["shared.up"], w["shared.down"])
     return out
@@ -194,8 +196,9 @@ def _sub(tensors, prefix, dtype):
             if k.startswith(prefix)}
 
 
-def forward(config, tensors, tokens, dtype=np.float64, layers_out=None, tap=None):
-    """Logits [T, vocab] of one sequence; layers_out (a list) receives the stream after every run."""
+def forward(config, tensors, tokens, dtype=np.float64, layers_out=None, margins=None):
+    """Logits [T, vocab] of one sequence; layers_out (a list) receives the stream after every run, margins (a list)
+    by how much every router chose."""
     eps = config["norm"]["eps"]
     m = config["residual_mult"]
     bg = config["embedding"]["bigram"]
@@ -211,7 +214,7 @@ def forward(config, tensors, tokens, dtype=np.float64, layers_out=None, tap=None
         h = over_rms(x, eps) * float(tensors[f"l{i}.norm1"])
         w = _sub(tensors, f"l{i}.mix.", dtype)
         if layer["type"] == "latent_attention":
-            y = latent_attention(h, w, layer["mixer"], eps, tap)
+            y = latent_attention(h, w, layer["mixer"], eps)
         elif layer["type"] == "hgrn2":
             y = hgrn2(h, w, layer["mixer"], eps)
         else:
@@ -224,7 +227,7 @@ def forward(config, tensors, tokens, dtype=np.float64, layers_out=None, tap=None
             if f["kind"] == "dense":
                 y = dense_ff(h, w, eps)
             elif f["kind"] == "moe":
-                y = moe_ff(h, w, f, tap)
+                y = moe_ff(h, w, f, margins)
             else:
                 raise ValueError(f["kind"])
             x = x + m * y
