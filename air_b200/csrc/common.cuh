@@ -45,7 +45,8 @@ __device__ __forceinline__ void trace_point(int id) {
 enum TraceId { TR_EMBED = 1, TR_NORM, TR_ROPE, TR_SILU, TR_CONVERT, TR_TABLE, TR_ATT_REF, TR_ATT_DECODE, TR_ATT_COMBINE,
                TR_ATT_PREFILL, TR_GEMM_F32, TR_GEMM_TC, TR_SAMPLE, TR_CONV, TR_SCAN, TR_GATED, TR_QKV_PREPARE,
                TR_GLU, TR_SCALED_NORM, TR_POST_NORM, TR_QK_NORMED_PREPARE, TR_LATENT_PREPARE, TR_MOE_ROUTE, TR_MOE_SORT,
-               TR_GROUPED_GEMM, TR_GATHER_KEYS, TR_MASKED_SOFTMAX, TR_ATT_GROUPED };
+               TR_GROUPED_GEMM, TR_GATHER_KEYS, TR_MASKED_SOFTMAX, TR_ATT_GROUPED, TR_POLYNORM, TR_STREAM_ADD,
+               TR_HEAD_GATE };
 
 __device__ __forceinline__ void pdl_enter(int id = 0) {
     pdl_trigger();

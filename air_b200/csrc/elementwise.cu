@@ -99,7 +99,7 @@ __global__ void remember_tokens_kernel(const int* __restrict__ resolved, const i
 // h[t, i] += again[t, i] + row[i] (each optional): what a run adds to the stream ahead of its layer.
 __global__ void stream_add_kernel(float* __restrict__ h, const float* __restrict__ again, const float* __restrict__ row,
                                   int E, size_t n) {
-    pdl_enter(TR_NORM);
+    pdl_enter(TR_STREAM_ADD);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         float x = h[i];
         if (again) x += again[i];

@@ -17,37 +17,77 @@
 
 namespace air {
 
-template <typename TO>
-__global__ void __launch_bounds__(256)
+// A block per row.  The row (with its bias) is kept in shared memory between the pass that takes the three sums of
+// squares and the pass that writes (ROW_IN_SMEM; rows too long for that are read again), four elements at a time
+// where the row's start and length allow (VEC).  Few rows (a decode step) get blocks of 1,024 threads, so that all of
+// a row's loads are under way at once.
+template <typename TO, bool VEC, bool ROW_IN_SMEM>
+__global__ void __launch_bounds__(1024)
 polynorm_kernel(const float* __restrict__ in, int ld, const float* __restrict__ bias, TO* __restrict__ out, int ldo,
                 int F, float a, float b, float c, float e, float eps) {
-    __shared__ float scratch[32];
-    pdl_enter(TR_GLU);
+    __shared__ float scratch[3][32];
+    extern __shared__ __align__(16) float zrow[];
+    pdl_enter(TR_POLYNORM);
     const int t = blockIdx.x;
     const float* row = in + (size_t)t * ld;
     float s2 = 0.f, s4 = 0.f, s6 = 0.f;
-    for (int i = threadIdx.x; i < F; i += blockDim.x) {
-        const float z = row[i] + (bias ? bias[i] : 0.f);
+    auto take = [&](float z) {
         const float z2 = z * z;
         s2 += z2;
         s4 = fmaf(z2, z2, s4);
         s6 = fmaf(z2 * z, z2 * z, s6);
+    };
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < F; i += blockDim.x * 4) {
+            float z[4], bv[4] = {0.f, 0.f, 0.f, 0.f};
+            load4(row + i, z);
+            if (bias) load4(bias + i, bv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                z[j] += bv[j];
+                take(z[j]);
+            }
+            if (ROW_IN_SMEM) store4(zrow + i, z);
+        }
+    } else {
+        for (int i = threadIdx.x; i < F; i += blockDim.x) {
+            const float z = row[i] + (bias ? bias[i] : 0.f);
+            take(z);
+            if (ROW_IN_SMEM) zrow[i] = z;
+        }
     }
-    s2 = block_sum(s2, scratch);
-    s4 = block_sum(s4, scratch);
-    s6 = block_sum(s6, scratch);
+    // the three sums over the block, in an order that depends on the block's size only
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+    s2 = warp_sum(s2); s4 = warp_sum(s4); s6 = warp_sum(s6);
+    if (lane == 0) { scratch[0][warp] = s2; scratch[1][warp] = s4; scratch[2][warp] = s6; }
+    __syncthreads();
+    s2 = s4 = s6 = 0.f;
+    for (int i = 0; i < warps; ++i) { s2 += scratch[0][i]; s4 += scratch[1][i]; s6 += scratch[2][i]; }
     const float r1 = a / sqrtf(s2 / (float)F + eps), r2 = b / sqrtf(s4 / (float)F + eps),
                 r3 = c / sqrtf(s6 / (float)F + eps);
     TO* dst = out + (size_t)t * ldo;
-    for (int i = threadIdx.x; i < ldo; i += blockDim.x) {
-        float y = i == F ? 1.f : 0.f;
-        if (i < F) {
-            const float z = row[i] + (bias ? bias[i] : 0.f);
-            const float z2 = z * z;
-            y = z * r1 + z2 * r2 + z2 * z * r3 + e;
+    auto act = [&](float z) {
+        const float z2 = z * z;
+        return z * r1 + z2 * r2 + z2 * z * r3 + e;
+    };
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < F; i += blockDim.x * 4) {
+            float z[4], bv[4] = {0.f, 0.f, 0.f, 0.f};
+            if (ROW_IN_SMEM) {
+                load4(zrow + i, z);
+            } else {
+                load4(row + i, z);
+                if (bias) load4(bias + i, bv);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) z[j] = act(z[j] + bv[j]);
+            store4(dst + i, z);
         }
-        dst[i] = from_float<TO>(y);
+    } else {
+        for (int i = threadIdx.x; i < F; i += blockDim.x)
+            dst[i] = from_float<TO>(act(ROW_IN_SMEM ? zrow[i] : row[i] + (bias ? bias[i] : 0.f)));
     }
+    for (int i = F + threadIdx.x; i < ldo; i += blockDim.x) dst[i] = from_float<TO>(i == F ? 1.f : 0.f);
 }
 
 template <typename TI, typename TO>
@@ -71,7 +111,7 @@ __global__ void glu_kernel(const TI* __restrict__ in, TO* __restrict__ out, int 
 template <typename TX>
 __global__ void head_gate_kernel(TX* __restrict__ x, const float* __restrict__ gate, const int* __restrict__ token_seq,
                                  int H, int d, size_t total) {
-    pdl_enter(TR_GLU);
+    pdl_enter(TR_HEAD_GATE);
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t th = idx / d;
         if (token_seq[th / H] < 0) continue;
@@ -134,8 +174,23 @@ AIR_API int air_polynorm(const float* in, int ld, const float* bias, void* out, 
                          float a, float b, float c, float e, float eps, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (F <= 0 || ldo < F || ld < F) return AIR_ERR_BAD_ARGUMENT;
-    AIR_DISPATCH(out_dtype, TO, return air::launch(air::polynorm_kernel<TO>, T, 256, 0, stream, in, ld, bias, (TO*)out,
-                                                   ldo, F, a, b, c, e, eps));
+    const int threads = T <= 296 ? 1024 : 256;
+    const bool vec = F % 4 == 0 && ld % 4 == 0 && ldo % 4 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+                     (!bias || ((uintptr_t)bias & 15) == 0);
+    const size_t row_bytes = sizeof(float) * (size_t)F;
+    const bool in_smem = row_bytes <= 160 * 1024;
+    const size_t smem = in_smem ? row_bytes : 0;
+    AIR_DISPATCH(out_dtype, TO, {
+        auto go = [&](auto kernel) {
+            if (smem > 48 * 1024) {
+                cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (err != cudaSuccess) return (int)err;
+            }
+            return air::launch(kernel, T, threads, smem, stream, in, ld, bias, (TO*)out, ldo, F, a, b, c, e, eps);
+        };
+        if (vec) return in_smem ? go(air::polynorm_kernel<TO, true, true>) : go(air::polynorm_kernel<TO, true, false>);
+        return in_smem ? go(air::polynorm_kernel<TO, false, true>) : go(air::polynorm_kernel<TO, false, false>);
+    });
     return 0;
 }
 

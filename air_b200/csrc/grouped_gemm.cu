@@ -11,8 +11,9 @@
 //   with a_local the row slot - (the group's first slot); plus g * a_group_stride elements.
 //   Where a slot's row of C goes: with o_index, p = o_index[slot]: part p % o_div, row p / o_div of out
 //   [o_div, rows, N] (o_part_stride elements per part); else row `slot` (or, o_local, the row inside the group) plus
-//   g * o_group_stride.  With o_scale (and o_index) the row of C is multiplied by o_scale[o_index[slot]] in 32-bit
-//   before it is written (the weight of a token's choice on the expert's OUTPUT).
+//   g * o_group_stride.  With o_scale the row of C is multiplied, in 32-bit before it is written, by
+//   o_scale[o_index[slot]] (the weight of a token's choice on the expert's OUTPUT) or, without o_index, by
+//   o_scale[row * o_scale_ld + g] (a gate per token and head behind a product per head).
 //   Epilogue 0: C as float32 or in A's type.  Epilogue 1: W_g is [2 F, K], blocks of gate_block rows of the gate and
 //   as many of the linear branch in turn (gate_block = F: all gate rows, then all linear rows), the arrangement that
 //   the dense gated feed-forward uses; C [rows, F] = silu(gate) * linear in A's type.
@@ -36,7 +37,7 @@ struct GroupedArgs {
     const int* start; int rows_per_group; const int* tiles; const int* num_tiles;
     int N, K;
     int gate_block;      // epilogue 1: rows of W_g come in blocks of gate_block gate rows and as many linear rows in turn
-    const float* o_scale;
+    const float* o_scale; int o_scale_ld;
 };
 
 constexpr int GG_BM = 64, GG_BN = 64, GG_BK = 16;
@@ -83,6 +84,7 @@ grouped_gemm_kernel(const GroupedArgs p) {
                 if (p.o_scale) omul = p.o_scale[dst];
             } else {
                 o = (long long)(p.o_local ? slot - first : slot) * p.ldo + (long long)g * p.o_group_stride;
+                if (p.o_scale) omul = p.o_scale[(long long)(p.o_local ? slot - first : slot) * p.o_scale_ld + g];
             }
         }
         a_off[tid] = a;
@@ -224,6 +226,7 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
                 if (p.o_scale) omul = p.o_scale[dst];
             } else {
                 o = (long long)(p.o_local ? slot - first : slot) * p.ldo + (long long)g * p.o_group_stride;
+                if (p.o_scale) omul = p.o_scale[(long long)(p.o_local ? slot - first : slot) * p.o_scale_ld + g];
             }
         }
         a_off[tid] = a;
@@ -342,16 +345,17 @@ AIR_API int air_grouped_gemm(const void* A, long long lda, long long a_group_str
                              long long ldo, long long o_group_stride, const int* o_index, int o_div,
                              long long o_part_stride, int o_local, int out_f32, const int* start, int rows_per_group,
                              const int* tiles, const int* num_tiles, int max_tiles, int groups, int N, int K,
-                             int dtype, int epi, int gate_block, const float* o_scale, cudaStream_t stream) {
+                             int dtype, int epi, int gate_block, const float* o_scale, int o_scale_ld,
+                             cudaStream_t stream) {
     if (N <= 0 || K <= 0 || groups <= 0) return 0;
     if ((start != nullptr) != (tiles != nullptr) || (start && !num_tiles) || epi < 0 || epi > 1 ||
-        (a_index && a_div <= 0) || (o_index && o_div <= 0) || (a_scale && !a_index) || (o_scale && (!o_index || epi)))
+        (a_index && a_div <= 0) || (o_index && o_div <= 0) || (a_scale && !a_index) || (o_scale && epi))
         return AIR_ERR_BAD_ARGUMENT;
     if (epi == 1 && gate_block <= 0) gate_block = N;
     if (epi == 1 && N % gate_block) return AIR_ERR_BAD_ARGUMENT;
     air::GroupedArgs p{A, lda, a_group_stride, a_index, a_div, a_local, a_scale, W, w_group_stride, out, ldo,
                        o_group_stride, o_index, o_div, o_part_stride, o_local, out_f32, start, rows_per_group, tiles,
-                       num_tiles, N, K, gate_block, o_scale};
+                       num_tiles, N, K, gate_block, o_scale, o_scale_ld};
     const int row_tiles = start ? max_tiles : (rows_per_group + air::GG_BM - 1) / air::GG_BM;
     if (row_tiles <= 0) return 0;
     if (row_tiles > 65535 || groups > 65535) return AIR_ERR_BAD_ARGUMENT;

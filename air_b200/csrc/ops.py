@@ -55,7 +55,7 @@ _SIGNATURES = {
     "air_moe_sort": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "air_grouped_gemm": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_longlong,
                          c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int,
-                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "air_rows_by_index": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "air_planes_by_index": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "air_qkv_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
@@ -127,7 +127,7 @@ TRACE_NAMES = {1: "embedding", 2: "add_rmsnorm", 3: "qkv_rope_store", 4: "silu_m
                7: "attention_ref", 8: "decode_attention", 9: "decode_combine", 10: "prefill_attention", 11: "gemm_f32",
                12: "gemm_tc", 13: "sample", 14: "short_conv", 15: "linear_scan", 16: "gated_rmsnorm",
                17: "qkv_prepare", 18: "glu", 19: "scaled_norm", 20: "post_norm", 21: "qk_normed_prepare",
-               22: "latent_prepare", 23: "moe_route", 24: "moe_sort", 25: "grouped_gemm", 26: "gather_keys", 27: "masked_softmax", 28: "grouped_attention"}
+               22: "latent_prepare", 23: "moe_route", 24: "moe_sort", 25: "grouped_gemm", 26: "gather_keys", 27: "masked_softmax", 28: "grouped_attention", 29: "polynorm", 30: "stream_add", 31: "head_gate"}
 
 
 def set_trace(buffer: Optional[torch.Tensor]) -> None:
@@ -660,11 +660,12 @@ def moe_sort(expert, experts, start, pair_of_slot, tiles, num_tiles):
 
 def grouped_gemm(a, w, out, n, k, *, lda, ldo, groups, a_group_stride=0, o_group_stride=0, a_index=None, a_div=1,
                  a_scale=None, a_local=False, o_index=None, o_div=1, o_part_stride=0, o_local=False, start=None,
-                 rows_per_group=0, tiles=None, num_tiles=None, silu_mul=False, gate_block=0, o_scale=None):
+                 rows_per_group=0, tiles=None, num_tiles=None, silu_mul=False, gate_block=0, o_scale=None, o_scale_ld=0):
     """out rows = a rows @ w[g]^T for every group g (w [groups, n (2n with silu_mul), k]); see grouped_gemm.cu for how
     rows are found.  Strides in elements.  out is float32 or of a's type; with silu_mul out = silu(gate) * linear, the
     rows of w[g] being blocks of gate_block gate rows and as many linear rows in turn (0: all gate rows first).
-    o_scale float32 (with o_index): the row written for slot s is multiplied by o_scale[o_index[s]], in 32-bit."""
+    o_scale float32: the row written for slot s is multiplied, in 32-bit, by o_scale[o_index[s]], or without o_index by
+    o_scale[row * o_scale_ld + g] (row: the row of out, inside the group where o_local)."""
     _req(a, "a", _FLOATS)
     _req(w, "w", (a.dtype,), (groups, 2 * n if silu_mul else n, k))
     _req(out, "out", (torch.float32, a.dtype))
@@ -683,7 +684,7 @@ def grouped_gemm(a, w, out, n, k, *, lda, ldo, groups, a_group_stride=0, o_group
         w.data_ptr(), w.shape[1] * w.shape[2], out.data_ptr(), int(ldo), int(o_group_stride), _ptr(o_index), int(o_div),
         int(o_part_stride), 1 if o_local else 0, 1 if out.dtype == torch.float32 else 0, _ptr(start),
         int(rows_per_group), _ptr(tiles), _ptr(num_tiles), tiles.shape[0] if tiles is not None else 0, int(groups),
-        int(n), int(k), _DT[a.dtype], 1 if silu_mul else 0, int(gate_block), _ptr(o_scale), _stream()), "grouped_gemm")
+        int(n), int(k), _DT[a.dtype], 1 if silu_mul else 0, int(gate_block), _ptr(o_scale), int(o_scale_ld), _stream()), "grouped_gemm")
     return out
 
 

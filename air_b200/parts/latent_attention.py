@@ -124,7 +124,5 @@ class LatentAttention(PortionAttention, Mixer):
         self.attend(q_full, latent.rows, bt, ctx, summed, latent=True)
         out = torch.empty((T, H, dv), dtype=rt.dtype, device=dev)
         ops.grouped_gemm(summed, self.uv, out, dv, R, lda=H * R, ldo=H * dv, groups=H, a_group_stride=R,
-                         o_group_stride=dv, a_local=True, o_local=True, rows_per_group=T)
-        if gate is not None:
-            ops.head_gate(out, gate, ctx.token_seq)
+                         o_group_stride=dv, a_local=True, o_local=True, rows_per_group=T, o_scale=gate, o_scale_ld=H)
         return self.o.f32_sums(out.view(T, H * dv))

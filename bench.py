@@ -496,6 +496,27 @@ def _tomodra(width, layers, heads, kv_heads, ff, vocab=32000):
             "layers": [dict(att if i % 3 == 2 else latent(i), mlp=mlp) for i in range(layers)]}
 
 
+# Pefivik beside Tomodra, the closest of the other designs (attention over a latent, a mixture of experts), at equal
+# width, heads, feed-forward and number of runs (`--design pefivik`): latent attention without positions over a latent
+# of 512 with a sink and gates, an HGRN2 layer in every fourth place, dense PolyNorm feed-forwards and mixtures of 16
+# experts of ff / 4 in 4 groups (2 take part, a token takes 2) with a shared expert of ff / 2 in turn; two of its layers
+# run twice, so `layers` runs are layers - 2 layers' weights.
+def _pefivik(width, layers, heads, kv_heads, ff, vocab=32000):
+    latent = {"type": "latent_attention", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": 512,
+                                                    "scale": 128 ** -0.5}}
+    hgrn = {"type": "hgrn2", "mixer": {"heads": heads, "dim": 128, "vdim": 128}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 16, "top": 2, "scale": 1.5,
+                                                                "groups": {"count": 4, "keep": 2}},
+           "shared": {"ff": ff // 2}}
+    n = max(2, layers - 2)
+    start = min(1, n - 2)
+    return {"architecture": "Pefivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.7,
+            "logit_softcap": 30.0, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 7}},
+            "loop": {"start": start, "stop": start + 2, "times": 2},
+            "layers": [dict(hgrn if i % 4 == 2 else latent, mlp=moe if i % 2 else dense) for i in range(n)]}
+
+
 def _qwen(width, layers, heads, kv_heads, ff, vocab=32000):
     return dict(_QWEN, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
                 num_key_value_heads=kv_heads, intermediate_size=ff, rms_norm_eps=1e-5, max_window_layers=layers,
@@ -823,26 +844,189 @@ def tomodra_kernels(width, heads, kv_heads, ff, T, batch, context):
     return rows
 
 
+def pefivik_kernels(width, heads, kv_heads, ff, T, batch, context):
+    """Pefivik's kernels alone at the layer's shapes, each beside the like kernel of Tomodra, Bivizen or the Qwen2
+    decoder, from memory (512 MB written before each launch, the writes' own time subtracted): microseconds, and the
+    share of the measured copy rate (bytes) or of the measured bf16 rate (flops) that the algorithm's bytes or flops
+    make."""
+    import torch
+    from air_b200.csrc import ops
+    pk = peaks()
+    big = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+
+    def graph_time(calls, reps=5):
+        for c in calls:
+            c()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(reps):
+                for c in calls:
+                    c()
+        graph.replay()
+        torch.cuda.synchronize()
+        us = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            us.append(a.elapsed_time(b) * 1e3 / reps)
+        return statistics.median(us)
+
+    flush = lambda: big.zero_()
+    t_flush = graph_time([flush])
+    rows = []
+
+    def report(name, f, nbytes=0, flops=0):
+        us = graph_time([flush, f]) - t_flush
+        frac = (nbytes / us / 1e3 / pk["hbm_gbs"]) if nbytes else (flops / us / 1e6 / pk["bf16_tflops"])
+        rows.append({"kernel": name, "us": round(us, 1), "of": "copy rate" if nbytes else "bf16 rate", "frac": round(frac, 3)})
+        print(f"  {name:66s} {us:8.1f} us  {frac:5.2f} of the measured {'copy' if nbytes else 'bf16'} rate", flush=True)
+
+    E, H, d, P, R = width, heads, 128, 64, 512
+    n_exp, top, F = 16, 2, ff // 4
+    dev, bf = "cuda", torch.bfloat16
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    for label, N, entries in (("prompt", T, [(0, T)]), ("decode", batch, [(context, 1)] * batch)):
+        print(f"{label}: {N} rows, width {E}, {H} heads of {d}, latent {R}, {n_exp} experts of {F} in 4 groups, top {top}")
+        S = len(entries)
+        starts = [0]
+        for _, n in entries:
+            starts.append(starts[-1] + n)
+        q_start, slots = i32(starts), i32(list(range(S)))
+        positions = torch.cat([torch.arange(p, p + n, dtype=torch.int32) for p, n in entries]).to(dev)
+        seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, (_, n) in enumerate(entries)]).to(dev)
+        per_request = -(-(max(p + n for p, n in entries)) // P)
+        bt = torch.arange(S * per_request, dtype=torch.int32, device=dev).view(S, per_request).contiguous()
+        # ---- the embedding with its table of pairs, beside the plain one
+        V, buckets = 32000, 65521
+        table, pairs = torch.randn(V, E, device=dev, dtype=bf), torch.randn(buckets + 1, E, device=dev, dtype=bf)
+        ids = torch.randint(0, V, (N,), dtype=torch.int32, device=dev)
+        previous, resolved = torch.zeros(S, 1, dtype=torch.int32, device=dev), torch.empty(N, dtype=torch.int32, device=dev)
+        h, h2 = torch.empty(N, E, device=dev), torch.empty(N, E, device=dev)
+        report("bigram_embedding (two rows in, the stream and a copy out) + remember_tokens",
+               lambda: (ops.bigram_embedding(table, pairs, ids, positions, seq, previous, h, h2, resolved, buckets, 127, 7),
+                        ops.remember_tokens(resolved, q_start, slots, previous, S)), N * E * 12)
+        report("  Qwen2: embedding", lambda: ops.embedding(table, ids, h), N * E * 6)
+        # ---- what a pass adds, and the norm that completes the stream with scaled sums
+        row, delta = torch.randn(E, device=dev), torch.randn(N, E, device=dev)
+        report("stream_add (the embedding's output again and a row)", lambda: ops.stream_add(h, h2, row), N * E * 12)
+        sc, w, x16 = torch.full((E,), 0.7, device=dev), torch.ones(E, device=dev, dtype=bf), torch.empty(N, E, device=dev, dtype=bf)
+        planes = torch.randn(top, N, E, device=dev)
+        report("scaled_norm (stream + m x one term, scalar norm)", lambda: ops.scaled_norm(h, [(delta, sc)], w, 1e-5, x16), N * E * 14)
+        report("scaled_norm (stream + m x (experts' planes + shared expert))", lambda: ops.scaled_norm(h, [(planes, sc), (delta, sc)], w, 1e-5, x16), N * E * (14 + 4 * top))
+        report("  Tomodra: post_norm (stream + planes + shared expert)", lambda: ops.post_norm(h, 3.0, planes, delta, None, w, 1e-5, x16), N * E * (14 + 4 * top))
+        report("  Qwen2: add_rmsnorm", lambda: ops.add_rmsnorm(h, delta, w, 1e-5, x16), N * E * 14)
+        # ---- from the first projection to queries, gates and the latent's pages
+        cols = -(-(H * d + R + H) // 8) * 8
+        proj, cw = torch.randn(N, cols, device=dev), torch.ones(R, device=dev)
+        rows_ = torch.zeros(S * per_request, P, R, device=dev, dtype=bf).normal_(0, 0.5)
+        q_plain, q_full = torch.empty(N, H, d, device=dev, dtype=bf), torch.empty(N, H, R, device=dev)
+        gate = torch.empty(N, H, device=dev)
+        report("latent_prepare (norm of the latent, gates, page write; no rotation)",
+               lambda: ops.latent_prepare(proj, cw, 1e-5, None, positions, seq, bt, q_plain, q_full, rows_, True, gate_out=gate, gate_column=H * d + R),
+               N * (cols * 4 + H * d * 2 + R * 2 + H * 4))
+        freq = torch.rand(32, device=dev, dtype=torch.float64)
+        proj_t = torch.randn(N, H * (d + 64) + R + 64, device=dev)
+        rows_t = torch.zeros(S * per_request, P, R + 64, device=dev, dtype=bf).normal_(0, 0.5)
+        q_full_t = torch.empty(N, H, R + 64, device=dev)
+        report("  Tomodra: latent_prepare (norm, rotation of 64, page write)",
+               lambda: ops.latent_prepare(proj_t, cw, 1e-5, freq, positions, seq, bt, q_plain, q_full_t, rows_t, True),
+               N * (proj_t.shape[1] * 4 + H * d * 2 + H * 64 * 4 + (R + 64) * 2))
+        out16 = torch.empty(N, H, d, device=dev, dtype=bf)
+        sums16, uv = torch.randn(N, H, R, device=dev).to(bf), torch.randn(H, d, R, device=dev, dtype=bf) * 0.05
+        report("grouped product: value expansion per head, the gate in its epilogue", lambda: ops.grouped_gemm(sums16, uv, out16, d, R, lda=H * R, ldo=H * d, groups=H, a_group_stride=R, o_group_stride=d, a_local=True, o_local=True, rows_per_group=N, o_scale=gate, o_scale_ld=H),
+               flops=2 * N * H * d * R)
+        report("  Tomodra: the same product without a gate", lambda: ops.grouped_gemm(sums16, uv, out16, d, R, lda=H * R, ldo=H * d, groups=H, a_group_stride=R, o_group_stride=d, a_local=True, o_local=True, rows_per_group=N),
+               flops=2 * N * H * d * R)
+        # ---- attention over the latent's rows
+        summed = torch.empty(N, H, R, device=dev, dtype=bf)
+        sink = torch.zeros(H, device=dev)
+        if label == "decode":
+            report("grouped_attention, latent rows of 512, all keys, sink", lambda: ops.grouped_attention(q_full, rows_, bt, seq, positions, summed, None, 0.09, latent=True, sink=sink),
+                   batch * (context + 1) * R * 2)
+            summed_t = torch.empty(N, H, R, device=dev, dtype=bf)
+            report("  Tomodra: grouped_attention, latent rows of 576, window 1,024", lambda: ops.grouped_attention(q_full_t, rows_t, bt, seq, positions, summed_t, 1024, 0.07, latent=True),
+                   batch * min(1024, context + 1) * (R + 64) * 2)
+        # ---- the state mixer: what the scan reads, the scan, the norm per head
+        Hs = H
+        xs = torch.randn(N, 3 * Hs * d, device=dev)
+        state, o = torch.zeros(S, Hs, d, d, device=dev), torch.empty(N, Hs, d, device=dev)
+        low, fb = torch.rand(Hs * d, device=dev) * 0.9, torch.zeros(Hs * d, device=dev)
+        scan_bytes = N * 4 * Hs * d * 4 + S * Hs * d * d * 8
+        report("linear_scan, HGRN2 (gate, lower bound, silu in the preparation)", lambda: ops.linear_scan(
+            ops.SCAN_HGRN, xs[:, :Hs * d], None, xs[:, 2 * Hs * d:], xs[:, Hs * d:2 * Hs * d], state, o, q_start, slots, seq,
+            lower=low, gate_bias=fb), scan_bytes)
+        xg = torch.randn(N, 4 * Hs * d, device=dev)
+        report("  Bivizen: linear_scan, gated linear attention (same sizes)", lambda: ops.linear_scan(
+            ops.SCAN_GLA, xg[:, :Hs * d], xg[:, Hs * d:2 * Hs * d], xg[:, 2 * Hs * d:3 * Hs * d], xg[:, 3 * Hs * d:], state, o,
+            q_start, slots, seq, q_scale=d ** -0.5, tau=16.0), scan_bytes + N * Hs * d * 4)
+        nw, yo = torch.ones(d, device=dev), torch.empty(N, Hs * d, dtype=bf, device=dev)
+        report("gated_rmsnorm without a gate (norm per head)", lambda: ops.gated_rmsnorm(o, None, nw, 1e-5, yo, seq), N * Hs * d * 6)
+        report("  Bivizen: gated_rmsnorm", lambda: ops.gated_rmsnorm(o, xg[:, :Hs * d], nw, 1e-5, yo, seq), N * Hs * d * 10)
+        # ---- the dense feed-forward's activation
+        z, ub = torch.randn(N, ff, device=dev), torch.randn(ff, device=dev)
+        act = torch.empty(N, ff + 8, device=dev, dtype=bf)
+        report("polynorm (float32 product and bias in, three norms)", lambda: ops.polynorm(z, ub, (1.0, 0.4, -0.1, 0.0), 1e-5, act, ff), N * ff * 6)
+        gu16, act2 = torch.randn(N, 2 * ff, device=dev).to(bf), torch.empty(N, ff, device=dev, dtype=bf)
+        report("  Qwen2: silu_mul (bfloat16 product in)", lambda: ops.silu_mul(gu16, act2, block=128), N * ff * 6)
+        gu32 = torch.randn(N, 2 * ff, device=dev)
+        report("  Bivizen: glu with limits (float32 product in)", lambda: ops.glu(gu32, act2, block=128, alpha=1.702, limit=7.0, shift=1.0), N * ff * 10)
+        # ---- the experts
+        x = torch.randn(N, E, device=dev, dtype=bf)
+        zr = torch.randn(N, 16, device=dev)
+        expert = torch.empty(N, top, dtype=torch.int32, device=dev)
+        weight = torch.empty(N, top, device=dev)
+        pairs_n = N * top
+        start, slots_ = torch.empty(n_exp + 1, dtype=torch.int32, device=dev), torch.empty(pairs_n, dtype=torch.int32, device=dev)
+        tiles_, count = torch.empty(pairs_n // 64 + n_exp, 2, dtype=torch.int32, device=dev), torch.empty(1, dtype=torch.int32, device=dev)
+        report("moe_route among the best 2 of 4 groups", lambda: ops.moe_route(zr, n_exp, top, expert, weight, None, renormalize=True, groups=4, keep=2, route_scale=1.5, norm_eps=1e-20), N * 16 * 4 + pairs_n * 8)
+        report("  Tomodra: moe_route", lambda: ops.moe_route(zr, n_exp, top, expert, weight, None), N * 16 * 4 + pairs_n * 8)
+        ops.moe_route(zr, n_exp, top, expert, weight, None, renormalize=True, groups=4, keep=2, route_scale=1.5, norm_eps=1e-20)
+        ops.moe_sort(expert, n_exp, start, slots_, tiles_, count)
+        down = torch.randn(n_exp, E, F, device=dev, dtype=bf) * 0.02
+        acts, y = torch.randn(pairs_n, F, device=dev, dtype=bf), torch.empty(top, N, E, device=dev)
+        if label == "decode":
+            used = len(set(expert.flatten().tolist()))
+            report(f"grouped product: down of {used} experts, the weight on the output", lambda: ops.grouped_gemm(acts, down, y, E, F, lda=F, ldo=E, groups=n_exp, o_index=slots_, o_div=top, o_part_stride=N * E, start=start, tiles=tiles_, num_tiles=count, o_scale=weight.view(-1)),
+                   used * F * E * 2)
+            report(f"  Tomodra: grouped product: down of {used} experts", lambda: ops.grouped_gemm(acts, down, y, E, F, lda=F, ldo=E, groups=n_exp, o_index=slots_, o_div=top, o_part_stride=N * E, start=start, tiles=tiles_, num_tiles=count),
+                   used * F * E * 2)
+        else:
+            ends = start[1:].clone()
+            report("experts: library grouped product for down, weighted rows back to planes", lambda: ops.planes_by_index(torch._grouped_mm(acts, down.transpose(1, 2), offs=ends), slots_, top, y, scale=weight.view(-1)),
+                   flops=2 * pairs_n * F * E)
+            report("  Tomodra: the same without the weight", lambda: ops.planes_by_index(torch._grouped_mm(acts, down.transpose(1, 2), offs=ends), slots_, top, y),
+                   flops=2 * pairs_n * F * E)
+    return rows
+
+
 def design_bench(args):
     import torch
     from air_b200.engine.batch import Entry, LAST_SAMPLED
-    designs = {"bivizen": ("Bivizen", _bivizen), "tomodra": ("Tomodra", _tomodra)}
+    designs = {"bivizen": ("Bivizen", _bivizen), "tomodra": ("Tomodra", _tomodra), "pefivik": ("Pefivik", _pefivik)}
+    # the model that stands beside the design: the Qwen2 decoder, or the closest of the other designs
+    beside = {"pefivik": ("tomodra", "Tomodra", _tomodra)}.get(args.design, ("qwen2", "Qwen2ForCausalLM", _qwen))
     if args.design not in designs:
         print(json.dumps({"error": f"--design {args.design}: the designs that are compared are {', '.join(designs)}"}))
         return 2
     title, make = designs[args.design]
-    record = {"design": title, "beside": "Qwen2ForCausalLM", "dtype": "bf16", "data": "synthetic", "sizes": {}}
+    record = {"design": title, "beside": beside[1], "dtype": "bf16", "data": "synthetic", "sizes": {}}
     context = args.context or 2048
     for name in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES):
         width, layers, heads, kv_heads, ff = DESIGN_SIZES[name]
         if args.layers:
             layers = args.layers
         size = {"width": width, "layers": layers, "heads": heads, "kv_heads": kv_heads, "ff": ff}
-        for label, cfg in ((args.design, make(width, layers, heads, kv_heads, ff)), ("qwen2", _qwen(width, layers, heads, kv_heads, ff))):
+        for label, cfg in ((args.design, make(width, layers, heads, kv_heads, ff)), (beside[0], beside[2](width, layers, heads, kv_heads, ff))):
             print(f"--- {label} at width {width}, {layers} layers", flush=True)
             size[label] = design_model(cfg, args, torch, Entry, LAST_SAMPLED)
         if not args.skip_kernels and args.design == "bivizen":
             size["kernels"] = design_kernels(width, heads, kv_heads, ff, args.prefill_tokens, args.batch, context)
+        if not args.skip_kernels and args.design == "pefivik":
+            size["kernels"] = pefivik_kernels(width, heads, kv_heads, ff, args.prefill_tokens, args.batch, context)
         if not args.skip_kernels and args.design == "tomodra":
             size["kernels"] = tomodra_kernels(width, heads, kv_heads, ff, args.prefill_tokens, args.batch, context)
         record["sizes"][name] = size
@@ -924,7 +1108,7 @@ def main():
     ap.add_argument("--skip-decode", action="store_true", help="for profiling the prefill step alone")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for ncu)")
     ap.add_argument("--kernel", default="", help="prefill_attention, or prompt_elementwise (at --prefill-tokens rows): time those kernels alone and exit")
-    ap.add_argument("--design", default="", help="bivizen or tomodra: prefill and decode of that design beside the Qwen2 decoder at "
+    ap.add_argument("--design", default="", help="bivizen, tomodra or pefivik: prefill and decode of that design beside the Qwen2 decoder (pefivik: beside Tomodra) at "
                     "equal sizes, and its kernels alone beside the like kernels (another line of output; the default "
                     "workload is not run)")
     ap.add_argument("--design-sizes", default="", help="with --design: which of the sizes 2048,4096 (default: both)")
