@@ -506,13 +506,13 @@ def _pefivik(width, layers, heads, kv_heads, ff, vocab=32000):
                                                     "scale": 128 ** -0.5}}
     hgrn = {"type": "hgrn2", "mixer": {"heads": heads, "dim": 128, "vdim": 128}}
     dense = {"kind": "dense", "ff": ff}
-    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 16, "top": 2, "scale": 1.5,
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 16, "top": 2, "scale": 2.0,
                                                                 "groups": {"count": 4, "keep": 2}},
            "shared": {"ff": ff // 2}}
     n = max(2, layers - 2)
     start = min(1, n - 2)
-    return {"architecture": "Pefivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.7,
-            "logit_softcap": 30.0, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 7}},
+    return {"architecture": "Pefivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "logit_softcap": 50.0, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 131, "mul_cur": 11}},
             "loop": {"start": start, "stop": start + 2, "times": 2},
             "layers": [dict(hgrn if i % 4 == 2 else latent, mlp=moe if i % 2 else dense) for i in range(n)]}
 
@@ -907,13 +907,13 @@ def pefivik_kernels(width, heads, kv_heads, ff, T, batch, context):
         previous, resolved = torch.zeros(S, 1, dtype=torch.int32, device=dev), torch.empty(N, dtype=torch.int32, device=dev)
         h, h2 = torch.empty(N, E, device=dev), torch.empty(N, E, device=dev)
         report("bigram_embedding (two rows in, the stream and a copy out) + remember_tokens",
-               lambda: (ops.bigram_embedding(table, pairs, ids, positions, seq, previous, h, h2, resolved, buckets, 127, 7),
+               lambda: (ops.bigram_embedding(table, pairs, ids, positions, seq, previous, h, h2, resolved, buckets, 131, 11),
                         ops.remember_tokens(resolved, q_start, slots, previous, S)), N * E * 12)
         report("  Qwen2: embedding", lambda: ops.embedding(table, ids, h), N * E * 6)
         # ---- what a pass adds, and the norm that completes the stream with scaled sums
         row, delta = torch.randn(E, device=dev), torch.randn(N, E, device=dev)
         report("stream_add (the embedding's output again and a row)", lambda: ops.stream_add(h, h2, row), N * E * 12)
-        sc, w, x16 = torch.full((E,), 0.7, device=dev), torch.ones(E, device=dev, dtype=bf), torch.empty(N, E, device=dev, dtype=bf)
+        sc, w, x16 = torch.full((E,), 0.5, device=dev), torch.ones(E, device=dev, dtype=bf), torch.empty(N, E, device=dev, dtype=bf)
         planes = torch.randn(top, N, E, device=dev)
         report("scaled_norm (stream + m x one term, scalar norm)", lambda: ops.scaled_norm(h, [(delta, sc)], w, 1e-5, x16), N * E * 14)
         report("scaled_norm (stream + m x (experts' planes + shared expert))", lambda: ops.scaled_norm(h, [(planes, sc), (delta, sc)], w, 1e-5, x16), N * E * (14 + 4 * top))

@@ -88,7 +88,7 @@ def random_config(seed):
         if u < 0.15:
             layers.append(bare(layer))
         elif u < 0.5:
-            layers.append(dense(layer, int(rng.choice([16, 40, 100, 256, 384]))))
+            layers.append(dense(layer, int(rng.choice([16, 40, 100, 256, 320]))))
         else:
             count = int(rng.choice([1, 2, 3, 4]))
             size = int(rng.choice([1, 2, 3, 4]))
@@ -96,7 +96,7 @@ def random_config(seed):
             top = int(rng.integers(1, keep * size + 1))
             layers.append(moe(layer, count * size, top, int(rng.choice([16, 24, 40, 64, 100])),
                               groups=(count, keep) if count > 1 or rng.random() < 0.5 else None,
-                              scale=float(rng.choice([0.5, 1.0, 1.5, 2.5])),
+                              scale=float(rng.choice([0.5, 1.0, 1.25, 2.5])),
                               shared=None if rng.random() < 0.3 else int(rng.choice([16, 40, 64, 96]))))
     n = len(layers)
     loop = None
@@ -104,8 +104,8 @@ def random_config(seed):
         start = int(rng.integers(0, n))
         loop = (start, int(rng.integers(start + 1, n + 1)), int(rng.choice([1, 2, 2, 3])))
     return config(int(rng.integers(50, 700)), width, float(rng.choice([1e-6, 1e-5, 1e-4])),
-                  float(rng.choice([0.4, 0.7, 1.0, 1.3])), float(rng.choice([0.0, 8.0, 30.0])),
-                  (int(rng.choice([1, 61, 509, 4099])), int(rng.choice([0, 1, 127, 65537])), int(rng.choice([1, 7, 31]))),
+                  float(rng.choice([0.4, 0.75, 1.0, 1.3])), float(rng.choice([0.0, 8.0, 20.0])),
+                  (int(rng.choice([1, 61, 521, 4099])), int(rng.choice([0, 1, 131, 65537])), int(rng.choice([1, 11, 31]))),
                   loop, layers)
 
 

@@ -88,7 +88,7 @@ def test_what_a_pass_adds_to_the_stream_and_the_scalar_norm_behind_scaled_sums()
     from air_b200.parts.norm import ScalarRMSNorm
     from air_b200.parts.spec import PartSpec
     rng = np.random.default_rng(1)
-    T, E, m, g, eps = 13, 72, 0.7, 1.3, 1e-5
+    T, E, m, g, eps = 13, 72, 0.65, 1.3, 1e-5
     h, x0, row = rng.normal(size=(T, E)), rng.normal(size=(T, E)), rng.normal(size=E)
     for again, r in ((x0, row), (None, row), (x0, None)):
         hd = dev(h)
@@ -124,7 +124,7 @@ def latent_weights(rng, E, H, d, dv, R, scale, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,d,dv,R,page", [(4, 24, 20, 40, 16), (1, 32, 40, 56, 16), (8, 64, 64, 128, 64), (3, 8, 8, 300, 16),
+@pytest.mark.parametrize("H,d,dv,R,page", [(4, 24, 20, 40, 16), (1, 32, 40, 56, 16), (8, 64, 48, 128, 64), (3, 8, 8, 300, 16),
                                             (5, 16, 12, 20, 32)])
 def test_latent_attention_without_positions_with_sink_and_gates(H, d, dv, R, page, dtype):
     """The mixer alone over a request of 330 tokens in portions and single tokens (the long portions take the road of
@@ -284,7 +284,7 @@ def test_dense_feed_forward_with_polynorm_and_biases(E, F, T, dtype):
     assert np.abs(got - want).max() < tol * max(1.0, np.abs(want).max())
 
 
-@pytest.mark.parametrize("n,count,keep,top", [(6, 3, 2, 2), (8, 2, 1, 3), (8, 8, 5, 4), (16, 4, 3, 4), (1, 1, 1, 1),
+@pytest.mark.parametrize("n,count,keep,top", [(6, 3, 2, 2), (8, 2, 1, 3), (8, 8, 5, 4), (16, 4, 2, 5), (1, 1, 1, 1),
                                               (12, 1, 1, 5), (130, 13, 4, 9)])
 def test_router_chooses_among_the_best_groups(n, count, keep, top):
     """Against the plain router: random logits, rows of equal logits (the lower index wins, for groups and experts),
