@@ -150,7 +150,7 @@ def pefivik_spec(config: PefivikConfig) -> ModelSpec:
     before it.  Every layer is a pre-norm block whose sub-layers' outputs are multiplied by one constant before they
     join the stream, and whose norms have ONE learned number each: x += m mixer(n1(x)); x += m ff(n2(x)).  The mixer is
     attention over a compressed latent without positions, with a sink in the softmax and a sigmoid gate per head, or
-    HGRN2 (a matrix state per head whose forget gate also says what is written); the feed-forward is a dense one with
+    HGRN2 (a matrix state per head; the complement of the forget gate stands where a key would); the feed-forward is a dense one with
     biases and the PolyNorm activation, or a mixture of gated experts chosen among the best groups, beside a shared
     expert.  A stretch of layers may run several times over with the same weights, every pass with a cache of its own;
     ahead of every pass the stream receives a row of the table loop.step, and ahead of every pass but the first the

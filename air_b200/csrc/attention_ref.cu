@@ -14,8 +14,8 @@
 // (negative: padding, skipped).
 // A query at position p sees keys max(0, p - window + 1) .. p (window 0: all keys); with mask_mode 1 `window` is the
 // size of a chunk instead, and the query sees the keys p - p % window .. p (those of its own chunk, counted from
-// position 0 of the request).  With `sink` (float32 [H]) the softmax's denominator holds one more term exp(sink[h]),
-// which has no key and no value and is not scaled.  With `latent` a page is [P, d] (one row per token, no heads): every
+// position 0 of the request).  With `sink` (float32 [H]) the softmax's denominator holds one more term exp(sink[h]):
+// a bare logit that `scale` does not touch and that brings nothing to the output.  With `latent` a page is [P, d] (one row per token, no heads): every
 // query head reads the same row as its key, and the row's first dv elements as its value.  q is float32 if q_f32,
 // else of the cache's type.
 // score = scale * q.k, and with softcap > 0 then softcap * tanh(score / softcap).  With `gate` [T, H] (float32) a

@@ -9,8 +9,8 @@
 //                       the partial sums of a split product, [parts, T, E], which are added in order), written back into
 //                       the stream h when no rows are named, and out = x / sqrt(mean(x^2) + eps) * w.  With `rows`
 //                       the kernel reads h[rows[r]] and leaves h alone.  Without w it only completes the stream.
-//   polynorm_kernel     out[t, :] = a N(z) + b N(z^2) + c N(z^3) + e over a token's F values z = in[t, :] + bias, powers
-//                       taken per element and N(u) = u / sqrt(mean(u^2) + eps); 32-bit, written in out's type.  out has
+//   polynorm_kernel     z = in[t, :] + bias; out[t, i] = a z_i / r1 + b z_i^2 / r2 + c z_i^3 / r3 + e with r_p = sqrt(mean_i(z_i^(2p))
+//                       + eps) over the row's F columns; 32-bit, written in out's type.  out has
 //                       ldo >= F columns: column F (if any) receives 1 and the ones behind it 0, so that a product
 //                       whose matrix holds a bias in column F adds that bias.
 #include "common.cuh"

@@ -5,8 +5,8 @@
 //   layer has one, the logit of a gate for a shared expert) to each token's `top` experts with the largest scores.
 //   score 0 is sigmoid(z), score 1 the softmax over the n logits; the weights are the chosen scores as they are, or
 //   (renormalize) divided by their sum (+ norm_eps), and then times route_scale.  Equal scores: the lower index wins.
-//   With groups > 1 the experts stand in `groups` equal groups of neighbours; a group's mark is the sum of its two
-//   largest scores (its only score where a group is one expert), and only the experts of the `keep` groups with the
+//   With groups > 1 experts g * (n / groups) .. (g + 1) * (n / groups) - 1 make group g; a group's mark is its best score
+//   plus its second best (its only score where a group is one expert), and only the experts of the `keep` groups with the
 //   largest marks (of equal marks the lower group) can be chosen.  One warp per token.
 //   Writes expert [T, top] int32, weight [T, top] float32 and gate [T] = sigmoid(z[n]).
 //

@@ -624,8 +624,8 @@ def moe_route(z, experts, top, expert_out, weight_out, gate_out=None, has_gate=F
     """z float32 [T, >= experts (+ 1)]: router logits.  expert_out int32 [T, top], weight_out float32 [T, top]: the
     experts with the largest scores (sigmoid(z), or softmax(z)) and those scores (divided by their sum + norm_eps where
     renormalize), times route_scale; gate_out float32 [T] = sigmoid(z[:, experts]) where has_gate, else 1.  groups > 1:
-    only the experts of the `keep` best of `groups` equal groups of neighbours can be chosen, a group's mark being the
-    sum of its two largest scores."""
+    the experts are cut into `groups` runs of experts / groups consecutive indices, a run's mark is its best score plus
+    its second best, and only experts of the `keep` runs with the highest marks can be chosen."""
     T = z.shape[0]
     _req(z, "z", (torch.float32,))
     _req(expert_out, "expert_out", _I32, (T, top))

@@ -9,8 +9,8 @@
 //   linear_scan_kernel       a state S [d, dv] per head, updated token by token, read out after each update:
 //                              DELTA  S = g S;  u = beta (v - S^T k);  S += k u^T;  o = S^T q   (one decay per head)
 //                              GLA    S = diag(alpha) S + k v^T;  o = S^T q                      (a decay per key channel)
-//                              HGRN   the same recurrence with k = 1 - alpha: the gate that forgets also says how
-//                                     much is written; alpha = l + (1 - l) sigmoid(z + bias) with a lower bound l per
+//                              HGRN   the same recurrence with k = 1 - alpha (the complement of the decay stands where
+//                                     a key would); alpha = l + (1 - l) sigmoid(z + bias) with a lower bound l per
 //                                     channel, q = silu(q)
 //                            Columns of S do not depend on one another, so a block takes a few of them and a column is
 //                            held in the registers of L lanes of one warp; the tokens of a portion are taken in order.

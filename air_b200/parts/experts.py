@@ -25,9 +25,9 @@ class RoutedExperts(FeedForward):
 
     Router: z = Wr x in 32-bit; scores s = sigmoid(z) (score "sigmoid") or softmax(z); the `top` largest are chosen
     (of equal scores the lower index); the weights are the chosen scores, divided by their sum (+ norm_eps) where
-    renormalize, times route_scale.  With groups = (count, keep) the experts stand in `count` equal groups of
-    neighbours, a group's mark is the sum of its two largest scores, and only experts of the `keep` groups with the
-    largest marks can be chosen.  With weight_on "input" (the default) the weight multiplies the expert's INPUT (the
+    renormalize, times route_scale.  With groups = (count, keep) experts g * (experts / count) .. (g + 1) * (experts /
+    count) - 1 make group g, a group's mark is its best score plus its second best, and only experts of the `keep`
+    groups with the highest marks can be chosen.  With weight_on "input" (the default) the weight multiplies the expert's INPUT (the
     scaled row is rounded to the compute dtype like any input of a product), which is not the same as weighting its
     output, since an expert is not linear; with "output" it multiplies the expert's output, in 32-bit.  expert(u) = Wdown (silu(Wgate u) *
     (Wup u)).  The shared expert (shared_intermediate > 0) has the same form and runs for every token; with shared_gate

@@ -128,9 +128,8 @@ class ClampedGLU(SwiGLU):
 
 @register_feed_forward("polynorm_mlp")
 class PolyNormMLP(FeedForward):
-    """down(act(up(x) + b_up)) + b_down with act = PolyNorm: a N(z) + b N(z^2) + c N(z^3) + e, where the powers are
-    taken element by element, N(u) = u / sqrt(mean(u^2) + eps) over a token's `intermediate` values, and (a, b, c, e)
-    are four learned numbers.  params: hidden, intermediate, eps.  Tensors: <prefix>up [intermediate, hidden], up.b
+    """down(act(up(x) + b_up)) + b_down with act = PolyNorm: y_i = a z_i / r1 + b z_i^2 / r2 + c z_i^3 / r3 + e with r_p = sqrt(mean_i(z_i^(2p)) + eps)
+    over the `intermediate` columns of one row, and (a, b, c, e) the four numbers of the tensor act.  params: hidden, intermediate, eps.  Tensors: <prefix>up [intermediate, hidden], up.b
     [intermediate], down [hidden, intermediate], down.b [hidden], act [4].
 
     z leaves the first product in 32-bit; one kernel adds b_up, takes the three norms and writes the activation in the

@@ -170,13 +170,14 @@ class GatedLinearAttention(_StateMixer):
 
 @register_mixer("hgrn2")
 class HGRN2(_StateMixer):
-    """Gated linear attention whose forget gate also decides what is written (HGRN2).  q = silu(W_q x) (heads x
+    """HGRN2: gated linear attention without a key projection; what a channel does not keep of its old state (1 - f) is
+    the share of the new value that it takes in.  q = silu(W_q x) (heads x
     head_dim), v = W_v x (heads x v_dim); per head and channel f = l + (1 - l) sigmoid(W_f x + b_f) with a learned lower
     bound l; per head and token
 
         S = diag(f) S + (1 - f) v^T;   o = S^T q
 
-    (no key, no other scale), then o / sqrt(mean(o^2) + eps) * norm over each head's v_dim numbers (one weight for all
+    (k is not a projection and q carries no factor), then o / sqrt(mean(o^2) + eps) * norm over each head's v_dim numbers (one weight for all
     heads, no gate) and the output projection.  S is the request's state, 32-bit, zero at its start.  The gate, its
     sigmoid and 1 - f are 32-bit; the recurrence is gated linear attention's with k = 1 - f.
 

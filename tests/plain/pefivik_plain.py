@@ -18,10 +18,10 @@ The design, in this file's notation.  x is the stream [T, E]; m is one constant 
   hgrn2             q = silu(x Wq^T) (H x dim), v = x Wv^T (H x vdim), f = l + (1 - l) sigmoid(x Wf^T + b_f) per head
                     and channel; S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T; o_t = S_t^T q_t; each head's o divided by its
                     root mean square (times w, one vector [vdim] for all heads); Wo.
-  dense             z = x Wup^T + b_up;  y = a N(z) + b N(z^2) + c N(z^3) + e with powers taken per element and
-                    N(u) = u / sqrt(mean(u^2) + eps) over the ff values of a token;  y Wdown^T + b_down.
-  moe               s = sigmoid(x Wr^T); the experts stand in `count` groups of neighbours, a group's mark is the sum of
-                    its two largest s, only the `keep` best groups take part; of their experts the `top` with the
+  dense             z = x Wup^T + b_up;  y_i = a z_i / r1 + b z_i^2 / r2 + c z_i^3 / r3 + e, r_p = sqrt(mean_i z_i^(2p) + eps)
+                    over the row's ff columns;  y Wdown^T + b_down.
+  moe               s = sigmoid(x Wr^T); consecutive experts make `count` groups of one size, a group's mark is its best
+                    s plus its second best, only the `keep` groups with the highest marks take part; of their experts the `top` with the
                     largest s are taken; weights = s / (sum of the taken s + 1e-20) * router_scale; y = sum_e weight_e
                     expert_e(x) + shared(x); expert(u) = (silu(u Wg^T) * (u Wu^T)) Wd^T.
   output            n(x) with final.norm, the output matrix, then cap * tanh(logits / cap).

@@ -130,7 +130,7 @@ def test_plain_mechanisms_against_closed_forms():
     y = plain.poly_norm(z, np.array([2.0, 3.0, 5.0, 7.0]), 0.0)
     n = lambda u: u / np.sqrt((u * u).mean(-1, keepdims=True))
     assert np.allclose(y, 2 * n(z) + 3 * n(z ** 2) + 5 * n(z ** 3) + 7)
-    # the router: groups of neighbours, the sum of a group's two largest, the best groups, then the best experts
+    # the router: groups of consecutive experts, marks from the best two scores, the best groups, then the best experts
     s = np.array([0.9, 0.1, 0.5, 0.45, 0.6, 0.3, 0.2, 0.8])
     assert plain.route(s, 2, 4, 2) == [0, 7]               # marks 1.0, 0.95, 0.9, 1.0: groups 0 and 3
     assert plain.route(s, 3, 4, 3) == [0, 7, 2]            # ... and group 1
