@@ -119,40 +119,88 @@ __global__ void head_gate_kernel(TX* __restrict__ x, const float* __restrict__ g
     }
 }
 
-template <typename TW, typename TO>
+// VEC: four columns per access (E and the parts' stride multiples of 4, all pointers on 16-byte boundaries).
+template <typename TW, typename TO, bool VEC>
 __global__ void scaled_norm_kernel(float* __restrict__ h, const float* __restrict__ a, const float* __restrict__ sa,
                                    int a_parts, const float* __restrict__ b, const float* __restrict__ sb, int b_parts,
                                    size_t part_stride, const TW* __restrict__ w, TO* __restrict__ out,
                                    const int* __restrict__ rows, int E, float eps) {
     __shared__ float scratch[32];
-    extern __shared__ float xrow[];
+    extern __shared__ __align__(16) float xrow[];
     pdl_enter(TR_SCALED_NORM);
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * E;
+    const bool keep = !rows && (a || b);
     float ss = 0.f;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) {
-        float x = h[src + i];
-        if (a) {
-            float t = a[src + i];
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < E; i += blockDim.x * 4) {
+            float x[4], t[4], u[4], sc[4];
+            load4(h + src + i, x);
+            if (a) {
+                load4(a + src + i, t);
 #pragma unroll 4
-            for (int p = 1; p < a_parts; ++p) t += a[p * part_stride + src + i];      // (loads ahead, sums in order)
-            x += (sa ? sa[i] : 1.f) * t;
-        }
-        if (b) {
-            float t = b[src + i];
+                for (int p = 1; p < a_parts; ++p) {                                   // (loads ahead, sums in order)
+                    load4(a + p * part_stride + src + i, u);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) t[j] += u[j];
+                }
+                if (sa) load4(sa + i, sc);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] += (sa ? sc[j] : 1.f) * t[j];
+            }
+            if (b) {
+                load4(b + src + i, t);
 #pragma unroll 4
-            for (int p = 1; p < b_parts; ++p) t += b[p * part_stride + src + i];
-            x += (sb ? sb[i] : 1.f) * t;
+                for (int p = 1; p < b_parts; ++p) {
+                    load4(b + p * part_stride + src + i, u);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) t[j] += u[j];
+                }
+                if (sb) load4(sb + i, sc);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] += (sb ? sc[j] : 1.f) * t[j];
+            }
+            store4(xrow + i, x);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ss += x[j] * x[j];
+            if (keep) store4(h + src + i, x);
         }
-        xrow[i] = x;
-        ss += x * x;
-        if (!rows && (a || b)) h[src + i] = x;
+    } else {
+        for (int i = threadIdx.x; i < E; i += blockDim.x) {
+            float x = h[src + i];
+            if (a) {
+                float t = a[src + i];
+#pragma unroll 4
+                for (int p = 1; p < a_parts; ++p) t += a[p * part_stride + src + i];
+                x += (sa ? sa[i] : 1.f) * t;
+            }
+            if (b) {
+                float t = b[src + i];
+#pragma unroll 4
+                for (int p = 1; p < b_parts; ++p) t += b[p * part_stride + src + i];
+                x += (sb ? sb[i] : 1.f) * t;
+            }
+            xrow[i] = x;
+            ss += x * x;
+            if (keep) h[src + i] = x;
+        }
     }
     if (!w) return;
     const float total = block_sum(ss, scratch);
     const float scale = rsqrtf(total / (float)E + eps);
-    for (int i = threadIdx.x; i < E; i += blockDim.x)
-        out[(size_t)r * E + i] = from_float<TO>(xrow[i] * scale * to_float(w[i]));
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < E; i += blockDim.x * 4) {
+            float x[4], wv[4];
+            load4(xrow + i, x);
+            load4(w + i, wv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[j] = x[j] * scale * wv[j];
+            store4(out + (size_t)r * E + i, x);
+        }
+    } else {
+        for (int i = threadIdx.x; i < E; i += blockDim.x)
+            out[(size_t)r * E + i] = from_float<TO>(xrow[i] * scale * to_float(w[i]));
+    }
 }
 
 }  // namespace air
@@ -213,11 +261,18 @@ AIR_API int air_scaled_norm(float* h, const float* a, const float* sa, int a_par
     if (R <= 256) threads = E / 2 >= 1024 ? 1024 : (E / 2 > threads ? (E / 2 + 31) / 32 * 32 : threads);
     const size_t smem = sizeof(float) * (size_t)E;
     if (smem > 200 * 1024) return AIR_ERR_BAD_ARGUMENT;
+    auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    const bool vec = E % 4 == 0 && part_stride % 4 == 0 && al(h) && al(a) && al(sa) && al(b) && al(sb) && al(w) && al(out);
     AIR_DISPATCH(w_dtype, TW, AIR_DISPATCH(out_dtype, TO, {
-        auto kernel = air::scaled_norm_kernel<TW, TO>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return air::launch(kernel, R, threads, smem, stream, h, a, sa, a_parts, b, sb, b_parts, (size_t)part_stride,
-                           (const TW*)w, (TO*)out, rows, E, eps);
+        auto go = [&](auto kernel) {
+            if (smem > 48 * 1024) {
+                cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (err != cudaSuccess) return (int)err;
+            }
+            return air::launch(kernel, R, threads, smem, stream, h, a, sa, a_parts, b, sb, b_parts, (size_t)part_stride,
+                               (const TW*)w, (TO*)out, rows, E, eps);
+        };
+        return vec ? go(air::scaled_norm_kernel<TW, TO, true>) : go(air::scaled_norm_kernel<TW, TO, false>);
     }));
     return 0;
 }
