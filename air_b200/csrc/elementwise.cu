@@ -44,7 +44,7 @@ __global__ void bigram_embedding_kernel(const TT* __restrict__ table, const TT* 
                                         const int* __restrict__ token_seq, const int* __restrict__ previous,
                                         const int* __restrict__ last_token, float* __restrict__ out,
                                         float* __restrict__ out2, int* __restrict__ resolved, int E, int V,
-                                        long long buckets, long long mul_prev, long long mul_cur, int* status) {
+                                        long long buckets, long long mul_prev, long long mul_cur, int* status, int vec) {
     pdl_wait();          // the step's first kernel: see embedding_kernel
     pdl_trigger();
     trace_point(TR_EMBED);
@@ -77,6 +77,20 @@ __global__ void bigram_embedding_kernel(const TT* __restrict__ table, const TT* 
     }
     const TT* row = table + (size_t)(ok ? id : 0) * E;
     const TT* pair = pairs + (size_t)r * E;
+    if (vec) {           // four columns at a time (E a multiple of 4, every row on a boundary of four elements)
+        for (int i = threadIdx.x * 4; i < E; i += blockDim.x * 4) {
+            float x[4] = {0.f, 0.f, 0.f, 0.f}, y[4];
+            if (ok) {
+                load4(row + i, x);
+                load4(pair + i, y);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] += y[j];
+            }
+            store4(out + (size_t)t * E + i, x);
+            if (out2) store4(out2 + (size_t)t * E + i, x);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < E; i += blockDim.x) {
         const float x = ok ? to_float(row[i]) + to_float(pair[i]) : 0.f;
         out[(size_t)t * E + i] = x;
@@ -98,8 +112,26 @@ __global__ void remember_tokens_kernel(const int* __restrict__ resolved, const i
 // ---------------------------------------------------------------- h += again + row
 // h[t, i] += again[t, i] + row[i] (each optional): what a run adds to the stream ahead of its layer.
 __global__ void stream_add_kernel(float* __restrict__ h, const float* __restrict__ again, const float* __restrict__ row,
-                                  int E, size_t n) {
+                                  int E, size_t n, int vec) {
     pdl_enter(TR_STREAM_ADD);
+    if (vec) {           // four columns at a time (E a multiple of 4, the tensors on 16-byte boundaries)
+        for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (size_t)gridDim.x * blockDim.x * 4) {
+            float x[4], y[4];
+            load4(h + i, x);
+            if (again) {
+                load4(again + i, y);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] += y[j];
+            }
+            if (row) {
+                load4(row + i % E, y);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] += y[j];
+            }
+            store4(h + i, x);
+        }
+        return;
+    }
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         float x = h[i];
         if (again) x += again[i];
@@ -812,9 +844,10 @@ AIR_API int air_bigram_embedding(const void* table, const void* pairs, int table
                                  cudaStream_t stream) {
     if (T <= 0) return 0;
     if (buckets <= 0 || mul_prev < 0 || mul_cur < 0 || !previous || !resolved) return AIR_ERR_BAD_ARGUMENT;
+    const int vec = E % 4 == 0 && (((uintptr_t)table | (uintptr_t)pairs | (uintptr_t)out | (uintptr_t)out2) & 15) == 0;
     AIR_DISPATCH(table_dtype, TT, return launch(bigram_embedding_kernel<TT>, T, 256, 0, stream, (const TT*)table,
                                                 (const TT*)pairs, ids, positions, token_seq, previous, last_token, out,
-                                                out2, resolved, E, V, buckets, mul_prev, mul_cur, status));
+                                                out2, resolved, E, V, buckets, mul_prev, mul_cur, status, vec));
     return 0;
 }
 
@@ -826,8 +859,10 @@ AIR_API int air_remember_tokens(const int* resolved, const int* q_start, const i
 
 AIR_API int air_stream_add(float* h, const float* again, const float* row, int E, long long n, cudaStream_t stream) {
     if (n <= 0 || (!again && !row)) return 0;
-    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-    return launch(stream_add_kernel, blocks, 256, 0, stream, h, again, row, E, (size_t)n);
+    const int vec = E % 4 == 0 && n % 4 == 0 && (((uintptr_t)h | (uintptr_t)again | (uintptr_t)row) & 15) == 0;
+    const long long work = vec ? n / 4 : n;
+    const int blocks = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
+    return launch(stream_add_kernel, blocks, 256, 0, stream, h, again, row, E, (size_t)n, vec);
 }
 
 AIR_API int air_add_parts(float* h, const void* delta, int delta_dtype, int parts, long long n, cudaStream_t stream) {

@@ -38,7 +38,31 @@ polynorm_kernel(const float* __restrict__ in, int ld, const float* __restrict__ 
         s6 = fmaf(z2 * z, z2 * z, s6);
     };
     if (VEC) {
-        for (int i = threadIdx.x * 4; i < F; i += blockDim.x * 4) {
+        // four accesses of a thread are issued before the first is used (the sums are taken in the order of the columns
+        // all the same): with one access under way per thread a block keeps too few bytes in flight to fill the memory
+        constexpr int U = 4;
+        const int step = blockDim.x * 4;
+        int i = threadIdx.x * 4;
+        for (; i + (U - 1) * step < F; i += U * step) {
+            float z[U][4], bv[U][4];
+#pragma unroll
+            for (int u = 0; u < U; ++u) load4(row + i + u * step, z[u]);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (bias) load4(bias + i + u * step, bv[u]);
+                else bv[u][0] = bv[u][1] = bv[u][2] = bv[u][3] = 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    z[u][j] += bv[u][j];
+                    take(z[u][j]);
+                }
+                if (ROW_IN_SMEM) store4(zrow + i + u * step, z[u]);
+            }
+        }
+        for (; i < F; i += step) {
             float z[4], bv[4] = {0.f, 0.f, 0.f, 0.f};
             load4(row + i, z);
             if (bias) load4(bias + i, bv);

@@ -21,7 +21,7 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, const float* __res
                       const double* __restrict__ freq, const int* __restrict__ positions,
                       const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_blocks,
                       TO* __restrict__ q_plain, float* __restrict__ q_full, TO* __restrict__ cache, int owns, int H,
-                      int d, int rot, int R, int P, float* __restrict__ gate_out, int gate_col, int* status) {
+                      int d, int rot, int R, int P, float* __restrict__ gate_out, int gate_col, int* status, int vec) {
     __shared__ float cs[128], sn[128];
     __shared__ float scratch[32];
     pdl_enter(TR_LATENT_PREPARE);
@@ -39,9 +39,18 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, const float* __res
     }
     __syncthreads();
     const int qw = d + rot;
-    for (int idx = threadIdx.x; idx < H * d; idx += blockDim.x) {
-        const int h = idx / d, i = idx % d;
-        q_plain[((size_t)t * H + h) * d + i] = from_float<TO>(in[h * qw + i]);
+    if (vec) {           // four numbers of a head at a time (d, rot and ld multiples of 4, 16-byte boundaries)
+        for (int idx = threadIdx.x * 4; idx < H * d; idx += blockDim.x * 4) {
+            const int h = idx / d, i = idx % d;
+            float x[4];
+            load4(in + h * qw + i, x);
+            store4(q_plain + ((size_t)t * H + h) * d + i, x);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < H * d; idx += blockDim.x) {
+            const int h = idx / d, i = idx % d;
+            q_plain[((size_t)t * H + h) * d + i] = from_float<TO>(in[h * qw + i]);
+        }
     }
     for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
         const int h = idx / half, j = idx % half;
@@ -62,10 +71,31 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, const float* __res
     TO* row = cache + ((size_t)page * P + pos % P) * (R + rot);
     const float* c = in + (size_t)H * qw;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < R; i += blockDim.x) ss += c[i] * c[i];
+    const bool vec_c = vec && R % 4 == 0;
+    if (vec_c) {
+        for (int i = threadIdx.x * 4; i < R; i += blockDim.x * 4) {
+            float x[4];
+            load4(c + i, x);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ss += x[j] * x[j];
+        }
+    } else {
+        for (int i = threadIdx.x; i < R; i += blockDim.x) ss += c[i] * c[i];
+    }
     const float total = block_sum(ss, scratch);
     const float scale = 1.f / sqrtf(total / (float)R + eps);
-    for (int i = threadIdx.x; i < R; i += blockDim.x) row[i] = from_float<TO>(c[i] * scale * c_w[i]);
+    if (vec_c) {
+        for (int i = threadIdx.x * 4; i < R; i += blockDim.x * 4) {
+            float x[4], wv[4];
+            load4(c + i, x);
+            load4(c_w + i, wv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[j] = x[j] * scale * wv[j];
+            store4(row + i, x);
+        }
+    } else {
+        for (int i = threadIdx.x; i < R; i += blockDim.x) row[i] = from_float<TO>(c[i] * scale * c_w[i]);
+    }
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
         const float u = c[R + j], v = c[R + j + half];
         row[R + j] = from_float<TO>(u * cs[j] - v * sn[j]);
@@ -84,10 +114,12 @@ AIR_API int air_latent_prepare(const float* proj, int ld, const float* c_w, floa
     if (rot < 0 || (rot & 1) || rot > 256 || (rot > 0 && !freq) || (owns && !c_w) || d <= 0 || R <= 0 ||
         (gate_out && (gate_col < H * (d + rot) + (owns ? R + rot : 0) || gate_col + H > ld)))
         return AIR_ERR_BAD_ARGUMENT;
+    const int vec = d % 4 == 0 && rot % 4 == 0 && ld % 4 == 0 &&
+                    (((uintptr_t)proj | (uintptr_t)c_w | (uintptr_t)q_plain | (uintptr_t)cache) & 15) == 0;
     AIR_DISPATCH(out_dtype, TO, return air::launch(air::latent_prepare_kernel<TO>, T, 256, 0, stream, proj, ld, c_w, eps,
                                                    freq, positions, token_seq, block_table, max_blocks, (TO*)q_plain,
                                                    q_full, (TO*)cache, owns, H, d, rot, R, P, gate_out, gate_col,
-                                                   status));
+                                                   status, vec));
     return 0;
 }
 

@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
 template <typename TO>
 __global__ void __launch_bounds__(128)
 gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gate, int ldg, const float* __restrict__ w,
-                     TO* __restrict__ out, const int* __restrict__ token_seq, int T, int H, int dv, float eps) {
+                     TO* __restrict__ out, const int* __restrict__ token_seq, int T, int H, int dv, float eps, int vec) {
     pdl_enter(TR_GATED);
     const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (item >= T * H) return;
@@ -322,6 +322,27 @@ gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gate
     if (token_seq[t] < 0) return;
     const float* row = o + (size_t)item * dv;
     float ss = 0.f;
+    if (vec) {           // four columns per lane and access (dv and ldg multiples of 4, the tensors on 16-byte boundaries)
+        for (int i = lane * 4; i < dv; i += 128) {
+            float x[4];
+            load4(row + i, x);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ss = fmaf(x[j], x[j], ss);
+        }
+        ss = warp_sum(ss);
+        const float scale = rsqrtf(ss / (float)dv + eps);
+        const float* gr = gate ? gate + (size_t)t * ldg + h * dv : nullptr;
+        for (int i = lane * 4; i < dv; i += 128) {
+            float x[4], wv[4], g[4];
+            load4(row + i, x);
+            load4(w + i, wv);
+            if (gr) load4(gr + i, g);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[j] = x[j] * scale * wv[j] * (gr ? silu_f(g[j]) : 1.f);
+            store4(out + (size_t)item * dv + i, x);
+        }
+        return;
+    }
     for (int i = lane; i < dv; i += 32) ss = fmaf(row[i], row[i], ss);
     ss = warp_sum(ss);
     const float scale = rsqrtf(ss / (float)dv + eps);
@@ -434,8 +455,10 @@ AIR_API int air_gated_rmsnorm(const float* o, const float* gate, int ldg, const 
                               const int* token_seq, int T, int H, int dv, float eps, cudaStream_t stream) {
     if (T <= 0) return 0;
     const int blocks = (T * H + 3) / 4;
+    const int vec = dv % 4 == 0 && (!gate || ldg % 4 == 0) &&
+                    (((uintptr_t)o | (uintptr_t)gate | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
     AIR_DISPATCH(out_dtype, TO, return air::launch(air::gated_rmsnorm_kernel<TO>, blocks, 128, 0, stream, o, gate, ldg, w,
-                                                   (TO*)out, token_seq, T, H, dv, eps));
+                                                   (TO*)out, token_seq, T, H, dv, eps, vec));
     return 0;
 }
 
