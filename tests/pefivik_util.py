@@ -48,6 +48,7 @@ def config(vocab, width, eps, mult, cap, bigram, loop, layers):
 #    than tokens.
 # B: no repeated stretch at all; one head; one expert of one (top == experts == 1, one group); a state mixer first and
 #    last; a dense layer whose ff is smaller than the width; no soft cap; no shared expert.
+# D: no size is a multiple of 4 (width, heads' sizes, the latent, ff): the kernels' roads of one element per access.
 # C: a stretch that is run once (it still adds its row), at the model's end; heads of 64 over a latent of 128 on
 #    pages of 64; groups of one expert each; every expert of the kept groups chosen.
 CONFIGS = {
@@ -66,8 +67,12 @@ CONFIGS = {
         dense(latent(4, 64, 64, 128, 0.11), 256),
         moe(latent(2, 32, 64, 64, 0.15), 8, 4, 64, groups=(8, 5), scale=1.2, shared=128),
         dense(hgrn(2, 64, 32), 192)]),
+    "D": config(150, 90, 1e-5, 0.8, 9.0, (77, 3, 5), (1, 3, 2), [
+        dense(latent(3, 10, 6, 18, 0.2), 50),
+        moe(hgrn(3, 10, 6), 6, 2, 30, groups=(3, 2), scale=1.0, shared=22),
+        dense(latent(2, 14, 10, 22, 0.2), 34)]),
 }
-SEEDS = {"A": 31, "B": 32, "C": 33}
+SEEDS = {"A": 31, "B": 32, "C": 33, "D": 34}
 
 
 def random_config(seed):

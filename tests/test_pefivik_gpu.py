@@ -355,7 +355,7 @@ def test_experts_weighted_on_their_output(n, count, keep, top, E, F, S, T, dtype
 
 
 # ----------------------------------------------------------------------------- whole models
-LENGTHS = {"A": (1, 7, 33, 97, 150), "B": (5, 40, 131, 64), "C": (2, 65, 150, 300)}
+LENGTHS = {"A": (1, 7, 33, 97, 150), "B": (5, 40, 131, 64), "C": (2, 65, 150, 300), "D": (3, 70, 1, 129)}
 
 
 def streams_for(name, seed=0, lengths=None):
@@ -368,7 +368,7 @@ def replay(name, dtype, steps, page_tokens=16, max_requests=4, peak_page=64):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_the_stream_after_every_run(name, dtype):
     """Layer by layer: the stream behind every run of the order list (a layer that runs three times counts three
     times) against the plain implementation's, for a prompt in one step."""
@@ -390,7 +390,7 @@ def test_the_stream_after_every_run(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_prompts(name, dtype):
     streams = streams_for(name)
     got, _ = replay(name, dtype, util.trace_whole(streams))
@@ -406,7 +406,7 @@ def test_prompt_then_token_by_token(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_portions_down_to_two_tokens(name, dtype):
     streams = streams_for(name, 20)
     got, _ = replay(name, dtype, util.trace_portions(streams))
@@ -417,7 +417,7 @@ def test_portions_down_to_two_tokens(name, dtype):
 
 @pytest.mark.parametrize("page", [16, 64])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_unequal_requests_together_with_pages_and_slots_used_again(name, dtype, page):
     """Ten requests through three slots and a pool that holds the peak only: every request must come out as it does
     alone (the oracle runs each alone), whatever shared its batches and whoever had its slot (the states of the state
