@@ -17,6 +17,28 @@
 
 namespace air {
 
+// The three sums over the block and, from them, the three factors a / r1, b / r2, c / r3: the first warp adds the
+// warps' sums (in an order that depends on the block's size only) and takes roots and quotients once for the block.
+__device__ __forceinline__ void polynorm_factors(float s2, float s4, float s6, float (*scratch)[32], int F, float a,
+                                                 float b, float c, float eps, float& r1, float& r2, float& r3) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+    s2 = warp_sum(s2); s4 = warp_sum(s4); s6 = warp_sum(s6);
+    if (lane == 0) { scratch[0][warp] = s2; scratch[1][warp] = s4; scratch[2][warp] = s6; }
+    __syncthreads();
+    if (warp == 0) {
+        s2 = warp_sum(lane < warps ? scratch[0][lane] : 0.f);
+        s4 = warp_sum(lane < warps ? scratch[1][lane] : 0.f);
+        s6 = warp_sum(lane < warps ? scratch[2][lane] : 0.f);
+        if (lane == 0) {
+            scratch[0][0] = a / sqrtf(s2 / (float)F + eps);
+            scratch[1][0] = b / sqrtf(s4 / (float)F + eps);
+            scratch[2][0] = c / sqrtf(s6 / (float)F + eps);
+        }
+    }
+    __syncthreads();
+    r1 = scratch[0][0]; r2 = scratch[1][0]; r3 = scratch[2][0];
+}
+
 // A block per row.  The row (with its bias) is kept in shared memory between the pass that takes the three sums of
 // squares and the pass that writes (ROW_IN_SMEM; rows too long for that are read again), four elements at a time
 // where the row's start and length allow (VEC).  Few rows (a decode step) get blocks of 1,024 threads, so that all of
@@ -80,15 +102,8 @@ polynorm_kernel(const float* __restrict__ in, int ld, const float* __restrict__ 
             if (ROW_IN_SMEM) zrow[i] = z;
         }
     }
-    // the three sums over the block, in an order that depends on the block's size only
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
-    s2 = warp_sum(s2); s4 = warp_sum(s4); s6 = warp_sum(s6);
-    if (lane == 0) { scratch[0][warp] = s2; scratch[1][warp] = s4; scratch[2][warp] = s6; }
-    __syncthreads();
-    s2 = s4 = s6 = 0.f;
-    for (int i = 0; i < warps; ++i) { s2 += scratch[0][i]; s4 += scratch[1][i]; s6 += scratch[2][i]; }
-    const float r1 = a / sqrtf(s2 / (float)F + eps), r2 = b / sqrtf(s4 / (float)F + eps),
-                r3 = c / sqrtf(s6 / (float)F + eps);
+    float r1, r2, r3;
+    polynorm_factors(s2, s4, s6, scratch, F, a, b, c, eps, r1, r2, r3);
     TO* dst = out + (size_t)t * ldo;
     auto act = [&](float z) {
         const float z2 = z * z;
@@ -110,6 +125,68 @@ polynorm_kernel(const float* __restrict__ in, int ld, const float* __restrict__ 
     } else {
         for (int i = threadIdx.x; i < F; i += blockDim.x)
             dst[i] = from_float<TO>(act(ROW_IN_SMEM ? zrow[i] : row[i] + (bias ? bias[i] : 0.f)));
+    }
+    for (int i = F + threadIdx.x; i < ldo; i += blockDim.x) dst[i] = from_float<TO>(i == F ? 1.f : 0.f);
+}
+
+// The same with the row in registers: K accesses of four columns per thread, all issued before the first is used, for
+// rows of up to 4 K blockDim columns (row start and length multiples of 4).  The sums are taken in the order of the
+// other form (a thread's columns ascending, then the block's warps in order).
+template <typename TO, int K>
+__global__ void __launch_bounds__(K > 4 ? 512 : 1024)
+polynorm_rows_kernel(const float* __restrict__ in, int ld, const float* __restrict__ bias, TO* __restrict__ out, int ldo,
+                     int F, float a, float b, float c, float e, float eps) {
+    __shared__ float scratch[3][32];
+    pdl_enter(TR_POLYNORM);
+    const int t = blockIdx.x;
+    const float* row = in + (size_t)t * ld;
+    const int step = blockDim.x * 4;
+    float z[K][4];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+        const int i = threadIdx.x * 4 + k * step;
+        if (i < F) load4(row + i, z[k]);
+        else z[k][0] = z[k][1] = z[k][2] = z[k][3] = 0.f;
+    }
+    if (bias) {
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const int i = threadIdx.x * 4 + k * step;
+            float bv[4];
+            if (i < F) {
+                load4(bias + i, bv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) z[k][j] += bv[j];
+            }
+        }
+    }
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+        if (threadIdx.x * 4 + k * step < F) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float z2 = z[k][j] * z[k][j];
+                s2 += z2;
+                s4 = fmaf(z2, z2, s4);
+                s6 = fmaf(z2 * z[k][j], z2 * z[k][j], s6);
+            }
+        }
+    }
+    float r1, r2, r3;
+    polynorm_factors(s2, s4, s6, scratch, F, a, b, c, eps, r1, r2, r3);
+    TO* dst = out + (size_t)t * ldo;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+        const int i = threadIdx.x * 4 + k * step;
+        if (i < F) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float v = z[k][j], v2 = v * v;
+                z[k][j] = v * r1 + v2 * r2 + v2 * v * r3 + e;
+            }
+            store4(dst + i, z[k]);
+        }
     }
     for (int i = F + threadIdx.x; i < ldo; i += blockDim.x) dst[i] = from_float<TO>(i == F ? 1.f : 0.f);
 }
@@ -249,6 +326,28 @@ AIR_API int air_polynorm(const float* in, int ld, const float* bias, void* out, 
     const int threads = T <= 296 ? 1024 : 256;
     const bool vec = F % 4 == 0 && ld % 4 == 0 && ldo % 4 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
                      (!bias || ((uintptr_t)bias & 15) == 0);
+    if (vec) {
+        // the row in registers: the fewest accesses per thread (1, 2, 4, 8) with which a block of at most `most` threads
+        // covers the row
+        // (many rows: narrow blocks where eight accesses a thread cover the row, so that an SM holds four blocks in
+        // different phases; few rows: wide blocks, so that a row's loads are all under way at once)
+        const int f4 = F / 4;
+        const int most = T <= 296 ? 1024 : ((f4 + 7) / 8 <= 256 ? 256 : 512);
+        for (int k = 1; k <= 8; k *= 2) {
+            if ((f4 + k - 1) / k > (k > 4 && most > 512 ? 512 : most)) continue;
+            int th = ((f4 + k - 1) / k + 31) / 32 * 32;
+            if (th < 128) th = 128;
+            AIR_DISPATCH(out_dtype, TO, {
+                auto run = [&](auto kernel) {
+                    return air::launch(kernel, T, th, 0, stream, in, ld, bias, (TO*)out, ldo, F, a, b, c, e, eps);
+                };
+                if (k == 1) return run(air::polynorm_rows_kernel<TO, 1>);
+                if (k == 2) return run(air::polynorm_rows_kernel<TO, 2>);
+                if (k == 4) return run(air::polynorm_rows_kernel<TO, 4>);
+                return run(air::polynorm_rows_kernel<TO, 8>);
+            });
+        }
+    }
     const size_t row_bytes = sizeof(float) * (size_t)F;
     const bool in_smem = row_bytes <= 160 * 1024;
     const size_t smem = in_smem ? row_bytes : 0;
