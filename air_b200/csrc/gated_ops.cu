@@ -12,7 +12,8 @@
 //   polynorm_kernel     z = in[t, :] + bias; out[t, i] = a z_i / r1 + b z_i^2 / r2 + c z_i^3 / r3 + e with r_p = sqrt(mean_i(z_i^(2p))
 //                       + eps) over the row's F columns; 32-bit, written in out's type.  out has
 //                       ldo >= F columns: column F (if any) receives 1 and the ones behind it 0, so that a product
-//                       whose matrix holds a bias in column F adds that bias.
+//                       whose matrix holds a bias in column F adds that bias.  polynorm_rows_kernel is the same with
+//                       the row in registers (rows that eight accesses of four columns per thread cover).
 #include "common.cuh"
 
 namespace air {
