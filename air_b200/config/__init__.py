@@ -2,6 +2,7 @@ from .model_config import ConfigError, Qwen2Config
 from .bivizen_config import BivizenConfig
 from .tomodra_config import TomodraConfig
 from .pefivik_config import PefivikConfig
+from .tabopel_config import TabopelConfig
 from . import architectures  # registers the known architectures
 import json
 import os

@@ -8,6 +8,7 @@ from ..parts.spec import BlockSpec, ModelSpec, PartSpec, RunStep
 from .bivizen_config import BivizenConfig
 from .model_config import Qwen2Config
 from .pefivik_config import PefivikConfig
+from .tabopel_config import TabopelConfig
 from .tomodra_config import TomodraConfig
 
 
@@ -201,3 +202,67 @@ def pefivik_spec(config: PefivikConfig) -> ModelSpec:
 
 
 register_architecture("Pefivik", PefivikConfig, pefivik_spec)
+
+
+def tabopel_spec(config: TabopelConfig) -> ModelSpec:
+    """Tabopel: the embedding's rows are multiplied by a constant.  Every layer has a norm on both sides of each
+    sub-layer: x += n1b(mixer(n1(x))); x += n2b(ff(n2(x))).  The mixer is grouped-query attention behind short causal
+    convolutions of q, k and v, with a sink of score 0 in the softmax and a sigmoid gate on the heads' outputs
+    ("attention"); grouped-query attention with biases, queries and keys normalised as whole vectors, a soft cap and a
+    learned sink per head ("attention_2"); or retention, linear attention with one constant decay per head
+    ("retention").  All three rotate the first part of a head, the first with frequencies that may be slowed down in
+    bands.  The feed-forward is a hidden layer with the squared rectifier, or a mixture of such experts chosen by
+    softmax score plus a learned correction, some of which may be identity experts.  A stretch of layers may run several
+    times over with the same weights, every pass with a cache of its own; ahead of every pass the stream receives a
+    row of the table loop.step.  Tensors: embed, loop.step, l<i>.norm1, norm1b, norm2, norm2b, l<i>.mix.*, l<i>.mlp.*,
+    final.norm, head."""
+    e = config.width
+    norm = PartSpec("rms", {"size": e, "eps": config.eps, "tensor": ""})
+    layers = []
+    for i, l in enumerate(config.layers):
+        position = None
+        if l.rot is not None and l.rot.dims:
+            position = PartSpec("rope_live", {"rotary_dim": l.rot.dims, "theta": l.rot.base, "pairing": "half",
+                                              "rule": "banded", "scaling": l.rot.scaling()})
+        if l.type == "retention":
+            mixer = PartSpec("retention", {"hidden": e, "heads": l.heads, "head_dim": l.dim, "v_dim": l.vdim,
+                                           "decay": l.decay, "eps": config.eps, "position": position})
+        else:
+            first = l.type == "attention"
+            mixer = PartSpec("normed_attention", {
+                "hidden": e, "heads": l.heads, "kv_heads": l.kv_heads, "head_dim": l.dim, "v_dim": l.vdim,
+                "scale": l.scale, "eps": config.eps,
+                "position": position or PartSpec("rope_live", {"rotary_dim": 0, "theta": 1.0}),
+                "qk_norm": False if first else "whole", "sink": "zero" if first else "learned",
+                "qkv_bias": not first, "conv": l.conv if first else 0, "softcap": 0.0 if first else l.softcap,
+                "out_gate": first})
+        parts = {"mixer_norm": norm, "mixer": mixer, "mixer_out_norm": norm}
+        names = {"mixer_norm": "norm1", "mixer": "mix.", "mixer_out_norm": "norm1b", "feed_forward_norm": "norm2",
+                 "feed_forward": "mlp.", "feed_forward_out_norm": "norm2b"}
+        f = l.mlp
+        if f is not None and f.kind == "dense":
+            parts["feed_forward"] = PartSpec("relu2_mlp", {"hidden": e, "intermediate": f.ff})
+        elif f is not None:
+            parts["feed_forward"] = PartSpec("routed_experts", {
+                "hidden": e, "experts": f.experts, "top": f.top, "intermediate": f.ff, "score": "softmax",
+                "renormalize": False, "weight_on": "output", "gated": False, "activation": "relu2",
+                "choice_bias": True, "identity": f.identity})
+        if f is not None:
+            parts["feed_forward_norm"] = parts["feed_forward_out_norm"] = norm
+        params = {"idle": tuple((n, (e,)) for n in l.idle)} if f is None and l.idle else {}
+        layers.append(BlockSpec(kind="sandwich", prefix=f"l{i}.", parts=parts, names=names, params=params))
+    order = [RunStep(i) for i in range(config.loop_start)]
+    tables = (("loop.step", config.loop_times),) if config.has_loop else ()
+    if config.loops:
+        for t in range(config.loop_times):
+            order += [RunStep(i, add_row=("loop.step", t) if i == config.loop_start else None)
+                      for i in range(config.loop_start, config.loop_stop)]
+    order += [RunStep(i) for i in range(config.loop_stop if config.loops else config.loop_start, len(layers))]
+    return ModelSpec(
+        architecture=config.architecture, hidden_size=e, vocab_size=config.vocab, max_positions=config.max_positions,
+        layers=tuple(layers), order=tuple(order), final_norm=norm, embedding_name="embed", final_norm_prefix="final.norm",
+        output_name="head", eos_token_id=config.eos_token_id, embedding_multiplier=config.embedding_scale,
+        stream_tables=tables)
+
+
+register_architecture("Tabopel", TabopelConfig, tabopel_spec)

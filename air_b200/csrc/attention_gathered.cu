@@ -10,7 +10,8 @@
 // masked_softmax_kernel: S [G, n * J, Lp] float32 (row (t, j): token t of the portion, head g * J + j) -> weights of the
 //   same shape in bfloat16.  Column c is the key at position lo + c; the query of token t stands at pos0 + t and sees
 //   keys up to its own: all, the last `window`, or (mask_mode 1) those of its chunk of `window` positions.  weights =
-//   exp(scale * s - m) / (sum + exp(sink_h - m)), the sink's term only where `sink` is given; 32-bit throughout,
+//   exp(scale * s - m) / (sum + exp(sink_h - m)), the sink's term only where `sink` is given (with a soft cap the
+//   score is cap * tanh(scale * s / cap)); 32-bit throughout,
 //   rounded once at the end.  Columns that are not seen, and L .. Lp, become 0.
 #include "common.cuh"
 
@@ -48,9 +49,12 @@ gather_keys_kernel(const T* __restrict__ cache, const int* __restrict__ block_ta
     }
 }
 
+// a score with a soft cap: cap * tanh(s / cap) where cap > 0, else the score itself
+__device__ __forceinline__ float soft_capped(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+
 __global__ void __launch_bounds__(256)
 masked_softmax_kernel(const float* __restrict__ S, __nv_bfloat16* __restrict__ W, int n, int J, int L, int Lp, int lo,
-                      int pos0, int window, int mask_mode, float scale, const float* __restrict__ sink) {
+                      int pos0, int window, int mask_mode, float scale, const float* __restrict__ sink, float softcap) {
     __shared__ float scratch[32];
     pdl_enter(TR_MASKED_SOFTMAX);
     const size_t r = blockIdx.x;
@@ -62,19 +66,19 @@ masked_softmax_kernel(const float* __restrict__ S, __nv_bfloat16* __restrict__ W
     __nv_bfloat16* w = W + r * Lp;
     const float sk = sink ? sink[g * J + j] : -INFINITY;
     float m = sk;
-    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) m = fmaxf(m, s[c] * scale);
+    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) m = fmaxf(m, soft_capped(s[c] * scale, softcap));
     m = warp_max(m);
     __syncthreads();
     if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
     __syncthreads();
     for (int i = 0; i < (int)(blockDim.x >> 5); ++i) m = fmaxf(m, scratch[i]);
     float sum = 0.f;
-    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) sum += expf(s[c] * scale - m);
+    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) sum += expf(soft_capped(s[c] * scale, softcap) - m);
     sum = block_sum(sum, scratch);
     if (sink) sum += expf(sk - m);
     const float inv = 1.f / sum;
     for (int c = threadIdx.x; c < Lp; c += blockDim.x)
-        w[c] = __float2bfloat16_rn(c >= c0 && c < c1 ? expf(s[c] * scale - m) * inv : 0.f);
+        w[c] = __float2bfloat16_rn(c >= c0 && c < c1 ? expf(soft_capped(s[c] * scale, softcap) - m) * inv : 0.f);
 }
 
 }  // namespace air
@@ -89,12 +93,12 @@ AIR_API int air_gather_keys(const void* cache, int dtype, const int* block_table
 }
 
 AIR_API int air_masked_softmax(const float* S, void* W, int G, int n, int J, int L, int Lp, int lo, int pos0, int window,
-                               int mask_mode, float scale, const float* sink, cudaStream_t stream) {
+                               int mask_mode, float scale, const float* sink, float softcap, cudaStream_t stream) {
     const long long rows = (long long)G * n * J;
     if (rows <= 0) return 0;
     if (rows > 2147483647LL || L > Lp) return AIR_ERR_BAD_ARGUMENT;
     return air::launch(air::masked_softmax_kernel, (unsigned)rows, 256, 0, stream, S, (__nv_bfloat16*)W, n, J, L, Lp, lo,
-                       pos0, window, mask_mode, scale, sink);
+                       pos0, window, mask_mode, scale, sink, softcap);
 }
 
 AIR_API int air_trace_set_attention_gathered(unsigned long long* buffer) { return air::set_trace_here(buffer); }

@@ -21,6 +21,10 @@
 
 namespace air {
 
+// a score with a soft cap: cap * tanh(s / cap) where cap > 0, else the score itself
+__device__ __forceinline__ float capped(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+
+
 constexpr int GA_KT = 64;                 // keys per tile
 
 template <typename T> struct Words;       // how elements lie in 32-bit words, and how many words of a value row a
@@ -46,7 +50,7 @@ __global__ void __launch_bounds__(256)
 grouped_attention_kernel(const void* __restrict__ q_any, int q_f32, const T* __restrict__ cache,
                          const int* __restrict__ block_table, int max_blocks, const int* __restrict__ token_seq,
                          const int* __restrict__ positions, float* __restrict__ part, int H, int G, int d, int dv, int P,
-                         int window, int mask_mode, float scale, int latent, int splits) {
+                         int window, int mask_mode, float scale, float softcap, int latent, int splits) {
     constexpr int JT = JB / 2, PER = Words<T>::per, NI = Words<T>::ni;
     extern __shared__ __align__(16) float smem[];
     pdl_enter(TR_ATT_GROUPED);
@@ -154,8 +158,8 @@ grouped_attention_kernel(const void* __restrict__ q_any, int q_f32, const T* __r
         __syncthreads();
         for (int j = warp; j < JB; j += 8) {
             const bool seen0 = key0 + lane >= lo && key0 + lane <= pos, seen1 = key0 + lane + 32 >= lo && key0 + lane + 32 <= pos;
-            const float s0 = seen0 ? (S[lane * JB + j] + S[(GA_KT + lane) * JB + j]) * scale : -INFINITY;
-            const float s1 = seen1 ? (S[(lane + 32) * JB + j] + S[(GA_KT + lane + 32) * JB + j]) * scale : -INFINITY;
+            const float s0 = seen0 ? capped((S[lane * JB + j] + S[(GA_KT + lane) * JB + j]) * scale, softcap) : -INFINITY;
+            const float s1 = seen1 ? capped((S[(lane + 32) * JB + j] + S[(GA_KT + lane + 32) * JB + j]) * scale, softcap) : -INFINITY;
             const float m_old = mrun[j];
             const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
             float p0 = 0.f, p1 = 0.f, c = 1.f;
@@ -245,7 +249,7 @@ __global__ void __launch_bounds__(256)
 grouped_attention_tc_kernel(const void* __restrict__ q_any, int q_f32, const __nv_bfloat16* __restrict__ cache,
                             const int* __restrict__ block_table, int max_blocks, const int* __restrict__ token_seq,
                             const int* __restrict__ positions, float* __restrict__ part, int H, int G, int d, int dv,
-                            int P, int window, int mask_mode, float scale, int latent, int splits, int stages) {
+                            int P, int window, int mask_mode, float scale, float softcap, int latent, int splits, int stages) {
     constexpr int JB = 16, PLD = GA_KT + 8;
     extern __shared__ __align__(16) float smem[];
     pdl_enter(TR_ATT_GROUPED);
@@ -373,8 +377,8 @@ grouped_attention_tc_kernel(const void* __restrict__ q_any, int q_f32, const __n
         __syncthreads();
         for (int j = warp; j < JB; j += 8) {
             const bool seen0 = key0 + lane >= lo && key0 + lane <= pos, seen1 = key0 + lane + 32 >= lo && key0 + lane + 32 <= pos;
-            const float s0 = seen0 ? S[j * GA_KT + lane] * scale : -INFINITY;
-            const float s1 = seen1 ? S[j * GA_KT + lane + 32] * scale : -INFINITY;
+            const float s0 = seen0 ? capped(S[j * GA_KT + lane] * scale, softcap) : -INFINITY;
+            const float s1 = seen1 ? capped(S[j * GA_KT + lane + 32] * scale, softcap) : -INFINITY;
             const float m_old = mrun[j];
             const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
             float p0 = 0.f, p1 = 0.f, c = 1.f;
@@ -470,7 +474,7 @@ grouped_combine_kernel(const float* __restrict__ part, const int* __restrict__ t
 template <typename T, int JB>
 int launch_grouped(const void* q, int q_f32, const void* cache, const int* block_table, int max_blocks,
                    const int* token_seq, const int* positions, float* part, int T_, int H, int G, int d, int dv, int P,
-                   int window, int mask_mode, float scale, int latent, int splits, cudaStream_t stream) {
+                   int window, int mask_mode, float scale, float softcap, int latent, int splits, cudaStream_t stream) {
     constexpr int PER = Words<T>::per;
     const int ksw = (d / PER) | 1, vsw = (dv / PER) | 1;
     const size_t smem = sizeof(float) * ((size_t)JB * d + 2 * JB * GA_KT + 3 * JB + GA_KT) +
@@ -481,7 +485,7 @@ int launch_grouped(const void* q, int q_f32, const void* cache, const int* block
     const int J = H / G;
     dim3 grid(T_, G * ((J + JB - 1) / JB), splits);
     return launch(kernel, grid, 256, smem, stream, q, q_f32, (const T*)cache, block_table, max_blocks, token_seq,
-                  positions, part, H, G, d, dv, P, window, mask_mode, scale, latent, splits);
+                  positions, part, H, G, d, dv, P, window, mask_mode, scale, softcap, latent, splits);
 }
 
 }  // namespace air
@@ -490,7 +494,7 @@ int launch_grouped(const void* q, int q_f32, const void* cache, const int* block
 AIR_API int air_grouped_attention(const void* q, int q_f32, const void* cache, int dtype, const int* block_table,
                                   int max_blocks, const int* token_seq, const int* positions, float* part, void* out,
                                   int T, int H, int G, int d, int dv, int P, int window, float scale, int mask_mode,
-                                  const float* sink, int latent, int splits, cudaStream_t stream) {
+                                  const float* sink, int latent, int splits, float softcap, cudaStream_t stream) {
     if (T <= 0) return 0;
     const int bytes = dtype == AIR_F32 ? 4 : 2;
     if (d <= 0 || dv <= 0 || dv > (dtype == AIR_F32 ? 768 : 1024) || (d * bytes) % 16 || (dv * bytes) % 16 || H <= 0 || G <= 0 ||
@@ -511,7 +515,7 @@ AIR_API int air_grouped_attention(const void* q, int q_f32, const void* cache, i
             if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             dim3 grid(T, G * ((J + 15) / 16), splits);
             rc = air::launch(kernel, grid, 256, smem, stream, q, q_f32, (const __nv_bfloat16*)cache, block_table,
-                             max_blocks, token_seq, positions, part, H, G, d, dv, P, window, mask_mode, scale, latent,
+                             max_blocks, token_seq, positions, part, H, G, d, dv, P, window, mask_mode, scale, softcap, latent,
                              splits, stages);
             if (rc) return rc;
             return air::launch(air::grouped_combine_kernel<__nv_bfloat16>, dim3(T, H), 128, 0, stream, part, token_seq,
@@ -521,10 +525,10 @@ AIR_API int air_grouped_attention(const void* q, int q_f32, const void* cache, i
     AIR_DISPATCH(dtype, TT, {
         if (J > 4)
             rc = air::launch_grouped<TT, 16>(q, q_f32, cache, block_table, max_blocks, token_seq, positions, part, T, H,
-                                             G, d, dv, P, window, mask_mode, scale, latent, splits, stream);
+                                             G, d, dv, P, window, mask_mode, scale, softcap, latent, splits, stream);
         else
             rc = air::launch_grouped<TT, 4>(q, q_f32, cache, block_table, max_blocks, token_seq, positions, part, T, H,
-                                            G, d, dv, P, window, mask_mode, scale, latent, splits, stream);
+                                            G, d, dv, P, window, mask_mode, scale, softcap, latent, splits, stream);
         if (rc) return rc;
         return air::launch(air::grouped_combine_kernel<TT>, dim3(T, H), 128, 0, stream, part, token_seq, sink, (TT*)out,
                            H, dv, splits);

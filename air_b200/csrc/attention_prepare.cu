@@ -105,7 +105,9 @@ AIR_API int air_trace_set_attention_prepare(unsigned long long* buffer) { return
 //   no norm); then the first `rot` elements are rotated, pair j by the angle position * freq[j], where pair j is
 //   (2j, 2j + 1) (pairing 1) or (j, j + rot/2) (pairing 0); cos and sin are multiplied by `magnitude`.  The angle is
 //   the product of the position and a 64-bit frequency, and its cos and sin are taken in 64-bit, once per token.
-//   v is copied.  Pages as above.
+//   v is copied.  Pages as above.  A bias (float32 [(H + G) dk + G dv]) is added to q, k and v first.  With `whole`
+//   the norm is taken over ALL heads of q at once (and all heads of k): x / sqrt(mean over H dk (x^2) + eps) * w with
+//   w of that whole size (q_w [H dk], k_w [G dk]).
 //
 // One block per token, one warp per head of q or k; a lane holds up to QKN_PAIRS pairs of its head.
 namespace air {
@@ -119,8 +121,8 @@ qk_normed_prepare_kernel(const float* __restrict__ proj, int ld, const float* __
                          int pairing, float magnitude, const int* __restrict__ positions,
                          const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_blocks,
                          TO* __restrict__ q_out, TO* __restrict__ cache, int H, int G, int dk, int dv, int P,
-                         int* status) {
-    __shared__ float cs[128], sn[128];
+                         int* status, const float* __restrict__ bias, int whole) {
+    __shared__ float cs[128], sn[128], scratch[32];
     pdl_enter(TR_QK_NORMED_PREPARE);
     const int t = blockIdx.x;
     const int slot = token_seq[t];
@@ -145,11 +147,24 @@ qk_normed_prepare_kernel(const float* __restrict__ proj, int ld, const float* __
         vdst = base + (size_t)G * P * dk + (size_t)(pos % P) * dv;
     }
     __syncthreads();
+    float whole_q = 1.f, whole_k = 1.f;
+    if (whole && q_w) {      // one scale for all heads of q and one for all heads of k
+        float sq = 0.f, sk = 0.f;
+        for (int i = threadIdx.x; i < (H + G) * dk; i += blockDim.x) {
+            const float v = in[i] + (bias ? bias[i] : 0.f);
+            if (i < H * dk) sq = fmaf(v, v, sq);
+            else sk = fmaf(v, v, sk);
+        }
+        whole_q = 1.f / sqrtf(block_sum(sq, scratch) / (float)(H * dk) + eps);
+        whole_k = 1.f / sqrtf(block_sum(sk, scratch) / (float)(G * dk) + eps);
+    }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int pairs = dk / 2;
     for (int head = warp; head < H + G; head += warps) {
         const float* x = in + (size_t)head * dk;
+        const float* hb = bias ? bias + (size_t)head * dk : nullptr;
         const float* w = head < H ? q_w : k_w;
+        if (w && whole) w += (size_t)(head < H ? head : head - H) * dk;
         float a[QKN_PAIRS], b[QKN_PAIRS];
         int ia[QKN_PAIRS], ib[QKN_PAIRS];
         float ss = 0.f;
@@ -161,13 +176,13 @@ qk_normed_prepare_kernel(const float* __restrict__ proj, int ld, const float* __
             if (j < pairs) {
                 ia[c] = (pairing == 0 && j < half) ? j : 2 * j;
                 ib[c] = (pairing == 0 && j < half) ? j + half : 2 * j + 1;
-                a[c] = x[ia[c]];
-                b[c] = x[ib[c]];
+                a[c] = x[ia[c]] + (hb ? hb[ia[c]] : 0.f);
+                b[c] = x[ib[c]] + (hb ? hb[ib[c]] : 0.f);
                 ss += a[c] * a[c] + b[c] * b[c];
             }
         }
         ss = warp_sum(ss);
-        const float scale = w ? 1.f / sqrtf(ss / (float)dk + eps) : 1.f;
+        const float scale = !w ? 1.f : whole ? (head < H ? whole_q : whole_k) : 1.f / sqrtf(ss / (float)dk + eps);
         TO* dst = head < H ? q_out + ((size_t)t * H + head) * dk
                            : (kdst ? kdst + (size_t)(head - H) * P * dk : nullptr);
 #pragma unroll
@@ -193,7 +208,8 @@ qk_normed_prepare_kernel(const float* __restrict__ proj, int ld, const float* __
     const int vcol = (H + G) * dk;
     if (vdst)
         for (int idx = threadIdx.x; idx < G * dv; idx += blockDim.x)
-            vdst[(size_t)(idx / dv) * P * dv + idx % dv] = from_float<TO>(in[vcol + idx]);
+            vdst[(size_t)(idx / dv) * P * dv + idx % dv] =
+                from_float<TO>(in[vcol + idx] + (bias ? bias[vcol + idx] : 0.f));
 }
 
 }  // namespace air
@@ -202,7 +218,7 @@ AIR_API int air_qk_normed_prepare(const float* proj, int ld, const float* q_w, c
                                   const double* freq, int rot, int pairing, float magnitude, const int* positions,
                                   const int* token_seq, const int* block_table, int max_blocks, void* q_out,
                                   void* cache, int out_dtype, int T, int H, int G, int dk, int dv, int P, int* status,
-                                  cudaStream_t stream) {
+                                  const float* bias, int whole, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (rot < 0 || rot > dk || (rot & 1) || (dk & 1) || rot > 256 || dk > 64 * air::QKN_PAIRS || (rot > 0 && !freq) ||
         pairing < 0 || pairing > 1 || (!q_w) != (!k_w))
@@ -210,6 +226,6 @@ AIR_API int air_qk_normed_prepare(const float* proj, int ld, const float* q_w, c
     AIR_DISPATCH(out_dtype, TO, return air::launch(air::qk_normed_prepare_kernel<TO>, T, 256, 0, stream, proj, ld, q_w,
                                                    k_w, eps, freq, rot, pairing, magnitude, positions, token_seq,
                                                    block_table, max_blocks, (TO*)q_out, (TO*)cache, H, G, dk, dv, P,
-                                                   status));
+                                                   status, bias, whole));
     return 0;
 }

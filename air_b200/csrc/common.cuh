@@ -46,7 +46,7 @@ enum TraceId { TR_EMBED = 1, TR_NORM, TR_ROPE, TR_SILU, TR_CONVERT, TR_TABLE, TR
                TR_ATT_PREFILL, TR_GEMM_F32, TR_GEMM_TC, TR_SAMPLE, TR_CONV, TR_SCAN, TR_GATED, TR_QKV_PREPARE,
                TR_GLU, TR_SCALED_NORM, TR_POST_NORM, TR_QK_NORMED_PREPARE, TR_LATENT_PREPARE, TR_MOE_ROUTE, TR_MOE_SORT,
                TR_GROUPED_GEMM, TR_GATHER_KEYS, TR_MASKED_SOFTMAX, TR_ATT_GROUPED, TR_POLYNORM, TR_STREAM_ADD,
-               TR_HEAD_GATE };
+               TR_HEAD_GATE, TR_SANDWICH_NORM, TR_RELU2 };
 
 __device__ __forceinline__ void pdl_enter(int id = 0) {
     pdl_trigger();

@@ -16,7 +16,8 @@
 //   o_scale[row * o_scale_ld + g] (a gate per token and head behind a product per head).
 //   Epilogue 0: C as float32 or in A's type.  Epilogue 1: W_g is [2 F, K], blocks of gate_block rows of the gate and
 //   as many of the linear branch in turn (gate_block = F: all gate rows, then all linear rows), the arrangement that
-//   the dense gated feed-forward uses; C [rows, F] = silu(gate) * linear in A's type.
+//   the dense gated feed-forward uses; C [rows, F] = silu(gate) * linear in A's type.  Epilogue 2: C = max(x, 0)^2 of the
+//   plain product x, in A's type (the hidden layer of an expert without a gate).
 //
 // Arithmetic.  float32 operands (and bfloat16 ones whose strides are not multiples of 8 elements): 32-bit multiply-adds
 // on the CUDA cores, k ascending; a tile is 64 x 64, a thread holds 4 x 4 of it (grouped_gemm_kernel).  bfloat16
@@ -156,6 +157,9 @@ grouped_gemm_kernel(const GroupedArgs p) {
             if (EPI == 1) {
                 const float gate = acc[0][i][j], lin = acc[EPI == 1 ? 1 : 0][i][j];
                 ((T*)p.out)[o + n] = from_float<T>(gate / (1.f + expf(-gate)) * lin);
+            } else if (EPI == 2) {
+                const float r = fmaxf(acc[0][i][j], 0.f);
+                ((T*)p.out)[o + n] = from_float<T>(r * r);
             } else if (p.out_f32) {
                 ((float*)p.out)[o + n] = acc[0][i][j] * om;
             } else {
@@ -325,10 +329,13 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
             for (int i = 0; i < 2; ++i) {
                 const int n = n0 + 8 * j + 2 * tq + i;
                 if (n >= N) continue;
-                const float v = acc[0][j][2 * half + i] * (EPI == 1 ? 1.f : om);
+                const float v = acc[0][j][2 * half + i] * (EPI == 0 ? om : 1.f);
                 if (EPI == 1) {
                     const float lin = acc[NW - 1][j][2 * half + i];
                     ((__nv_bfloat16*)p.out)[o + n] = __float2bfloat16_rn(v / (1.f + expf(-v)) * lin);
+                } else if (EPI == 2) {
+                    const float r = fmaxf(acc[0][j][2 * half + i], 0.f);
+                    ((__nv_bfloat16*)p.out)[o + n] = __float2bfloat16_rn(r * r);
                 } else if (p.out_f32) {
                     ((float*)p.out)[o + n] = v;
                 } else {
@@ -348,7 +355,7 @@ AIR_API int air_grouped_gemm(const void* A, long long lda, long long a_group_str
                              int dtype, int epi, int gate_block, const float* o_scale, int o_scale_ld,
                              cudaStream_t stream) {
     if (N <= 0 || K <= 0 || groups <= 0) return 0;
-    if ((start != nullptr) != (tiles != nullptr) || (start && !num_tiles) || epi < 0 || epi > 1 ||
+    if ((start != nullptr) != (tiles != nullptr) || (start && !num_tiles) || epi < 0 || epi > 2 ||
         (a_index && a_div <= 0) || (o_index && o_div <= 0) || (a_scale && !a_index) || (o_scale && epi))
         return AIR_ERR_BAD_ARGUMENT;
     if (epi == 1 && gate_block <= 0) gate_block = N;
@@ -369,10 +376,12 @@ AIR_API int air_grouped_gemm(const void* A, long long lda, long long a_group_str
             cudaFuncSetAttribute(air::grouped_gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             return air::launch(air::grouped_gemm_tc_kernel<1>, grid, 128, smem, stream, p);
         }
+        if (epi == 2) return air::launch(air::grouped_gemm_tc_kernel<2>, grid, 128, smem, stream, p);
         return air::launch(air::grouped_gemm_tc_kernel<0>, grid, 128, smem, stream, p);
     }
     AIR_DISPATCH(dtype, TT, {
         if (epi == 1) return air::launch(air::grouped_gemm_kernel<TT, 1>, grid, 256, 0, stream, p);
+        if (epi == 2) return air::launch(air::grouped_gemm_kernel<TT, 2>, grid, 256, 0, stream, p);
         return air::launch(air::grouped_gemm_kernel<TT, 0>, grid, 256, 0, stream, p);
     });
     return 0;

@@ -39,19 +39,24 @@ _SIGNATURES = {
                       c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "air_qk_normed_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_float, c_void_p,
                               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                              c_int, c_void_p, c_void_p],
+                              c_int, c_void_p, c_void_p, c_int, c_void_p],
     "air_latent_prepare": [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                            c_void_p, c_void_p],
     "air_grouped_attention": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_int,
-                              c_void_p],
+                              c_float, c_void_p],
     "air_gather_keys": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                         c_void_p, c_void_p],
     "air_masked_softmax": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                           c_void_p, c_void_p],
+                           c_void_p, c_float, c_void_p],
     "air_moe_route": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                      c_int, c_float, c_float, c_void_p],
+                      c_int, c_float, c_float, c_void_p, c_void_p],
+    "air_moe_identity": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "air_normed_add_norm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_float, c_void_p, c_void_p, c_int,
+                            c_void_p, c_int, c_int, c_float, c_void_p],
+    "air_relu2": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p],
+    "air_sigmoid_gate": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
     "air_moe_sort": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "air_grouped_gemm": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_longlong,
                          c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int,
@@ -62,10 +67,11 @@ _SIGNATURES = {
                         c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_void_p, c_void_p],
     "air_short_conv_silu": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                            c_int, c_void_p],
+                            c_int, c_int, c_void_p],
     "air_linear_scan": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_float, c_void_p],
+                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_float, c_void_p,
+                        c_void_p, c_int, c_float, c_void_p],
     "air_gated_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float,
                           c_void_p],
     "air_polynorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float,
@@ -127,7 +133,8 @@ TRACE_NAMES = {1: "embedding", 2: "add_rmsnorm", 3: "qkv_rope_store", 4: "silu_m
                7: "attention_ref", 8: "decode_attention", 9: "decode_combine", 10: "prefill_attention", 11: "gemm_f32",
                12: "gemm_tc", 13: "sample", 14: "short_conv", 15: "linear_scan", 16: "gated_rmsnorm",
                17: "qkv_prepare", 18: "glu", 19: "scaled_norm", 20: "post_norm", 21: "qk_normed_prepare",
-               22: "latent_prepare", 23: "moe_route", 24: "moe_sort", 25: "grouped_gemm", 26: "gather_keys", 27: "masked_softmax", 28: "grouped_attention", 29: "polynorm", 30: "stream_add", 31: "head_gate"}
+               22: "latent_prepare", 23: "moe_route", 24: "moe_sort", 25: "grouped_gemm", 26: "gather_keys", 27: "masked_softmax", 28: "grouped_attention", 29: "polynorm", 30: "stream_add", 31: "head_gate",
+               32: "normed_add_norm", 33: "relu2"}
 
 
 def set_trace(buffer: Optional[torch.Tensor]) -> None:
@@ -445,7 +452,7 @@ def grouped_attention_ok(cache_dtype, d, dv) -> bool:
 
 
 def grouped_attention(q, cache, block_table, token_seq, positions, out, window, scale, kv_heads=1, page_tokens=None,
-                      chunk=None, sink=None, latent=False, splits=None):
+                      chunk=None, sink=None, latent=False, splits=None, softcap=0.0):
     """paged_attention_ref's arithmetic and arguments (32-bit, any batch, window or chunk, sink, latent rows), by the
     kernel in which a block serves all query heads of a key/value head and the keys of a token are split over
     `splits` blocks (default: enough to fill the device); needs grouped_attention_ok(cache.dtype, d, dv)."""
@@ -484,7 +491,7 @@ def grouped_attention(q, cache, block_table, token_seq, positions, out, window, 
         q.data_ptr(), 1 if q.dtype == torch.float32 else 0, cache.data_ptr(), _DT[cache.dtype], block_table.data_ptr(),
         block_table.shape[1], token_seq.data_ptr(), positions.data_ptr(), part.data_ptr(), out.data_ptr(), T, H, G, d,
         dv, P, int(chunk or window or 0), float(scale), 1 if chunk else 0, _ptr(sink), 1 if latent else 0, int(splits),
-        _stream()), "grouped_attention")
+        float(softcap or 0.0), _stream()), "grouped_attention")
     global launches
     launches += 1
     return out
@@ -509,10 +516,12 @@ def gather_keys(cache, table_row, lo, count, keys, values, kv_heads=1, page_toke
                                    None if latent else values.data_ptr(), _stream()), "gather_keys")
 
 
-def masked_softmax(scores, weights, heads_per_group, lo, count, pos0, scale, window=None, chunk=None, sink=None):
+def masked_softmax(scores, weights, heads_per_group, lo, count, pos0, scale, window=None, chunk=None, sink=None,
+                   softcap=0.0):
     """scores float32 [G, n * J, Lp] -> weights bfloat16 of the same shape: the softmax of scale * scores over the keys
     that each row's query sees (column c = key lo + c, c < count; row (t, j) = the query at pos0 + t of head g * J + j),
-    with exp(sink[h]) in the denominator where sink (float32 [G * J]) is given."""
+    with exp(sink[h]) in the denominator where sink (float32 [G * J]) is given; with softcap > 0 a score is
+    softcap * tanh(scale * score / softcap)."""
     G, rows, Lp = scores.shape
     J = int(heads_per_group)
     _req(scores, "scores", (torch.float32,))
@@ -523,7 +532,7 @@ def masked_softmax(scores, weights, heads_per_group, lo, count, pos0, scale, win
         raise KernelError("masked_softmax: a window or a chunk, not both")
     _check(_get("air_masked_softmax")(scores.data_ptr(), weights.data_ptr(), G, rows // J, J, int(count), Lp, int(lo),
                                       int(pos0), int(chunk or window or 0), 1 if chunk else 0, float(scale), _ptr(sink),
-                                      _stream()), "masked_softmax")
+                                      float(softcap or 0.0), _stream()), "masked_softmax")
 
 
 def post_norm(h, alpha, a, b, b_row_scale, weight, eps, out):
@@ -552,19 +561,25 @@ def post_norm(h, alpha, a, b, b_row_scale, weight, eps, out):
 
 
 def qk_normed_prepare(proj, q_weight, k_weight, eps, freq, pairing, magnitude, positions, token_seq, block_table, q_out,
-                      cache, kv_heads, v_dim, page_tokens, status=None):
+                      cache, kv_heads, v_dim, page_tokens, status=None, bias=None, whole=False):
     """From the fused projection proj (float32 [T, (H + G) dk + G dv]: q, k, v per token) to q_out [T, H, dk] and
     the pages (keys [G, P, dk], then values [G, P, dv]).  q and k heads are normalised (x / sqrt(mean(x^2) + eps) * w,
     w float32 [dk]: q_weight for q, k_weight for k; None: no norm), then their first 2 * len(freq) elements are
     rotated by position * freq[j] (freq float64), pair j = (2j, 2j + 1) where pairing == "neighbours", (j, j + rot/2)
-    where "half"; cos and sin are multiplied by magnitude."""
+    where "half"; cos and sin are multiplied by magnitude.  bias (float32 [W]) is added to q, k and v first.  whole: the
+    norm is taken over all heads of q at once (and over all heads of k), with weights [H * dk] and [G * dk].  proj may be
+    a band of columns of a wider matrix."""
     T, H, dk = q_out.shape
     G, dv, P = int(kv_heads), int(v_dim), int(page_tokens)
     W = (H + G) * dk + G * dv
-    _req(proj, "proj", (torch.float32,), (T, W))
-    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+    pp, ld = _columns(proj, "proj")
+    if tuple(proj.shape) != (T, W):
+        raise KernelError(f"qk_normed_prepare: proj {tuple(proj.shape)}, wanted {(T, W)}")
+    for name, w, heads in (("q_weight", q_weight, H), ("k_weight", k_weight, G)):
         if w is not None:
-            _req(w, name, (torch.float32,), (dk,))
+            _req(w, name, (torch.float32,), (heads * dk if whole else dk,))
+    if bias is not None:
+        _req(bias, "bias", (torch.float32,), (W,))
     rot = 0
     if freq is not None:
         _req(freq, "freq", (torch.float64,))
@@ -579,10 +594,10 @@ def qk_normed_prepare(proj, q_weight, k_weight, eps, freq, pairing, magnitude, p
     if cache[0].numel() != G * P * (dk + dv):
         raise KernelError(f"qk_normed_prepare: a page of {cache[0].numel()} elements, not {G} x {P} x ({dk} + {dv})")
     _check(_get("air_qk_normed_prepare")(
-        proj.data_ptr(), W, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(freq), rot,
+        pp, ld, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(freq), rot,
         1 if pairing == "neighbours" else 0, float(magnitude), positions.data_ptr(), token_seq.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], q_out.data_ptr(), cache.data_ptr(), _DT[q_out.dtype], T, H, G, dk,
-        dv, P, _ptr(status), _stream()), "qk_normed_prepare")
+        dv, P, _ptr(status), _ptr(bias), 1 if whole else 0, _stream()), "qk_normed_prepare")
     return q_out
 
 
@@ -620,13 +635,16 @@ def latent_prepare(proj, c_weight, eps, freq, positions, token_seq, block_table,
 
 
 def moe_route(z, experts, top, expert_out, weight_out, gate_out=None, has_gate=False, score="sigmoid",
-              renormalize=False, groups=0, keep=0, route_scale=1.0, norm_eps=0.0):
+              renormalize=False, groups=0, keep=0, route_scale=1.0, norm_eps=0.0, choice_bias=None):
     """z float32 [T, >= experts (+ 1)]: router logits.  expert_out int32 [T, top], weight_out float32 [T, top]: the
     experts with the largest scores (sigmoid(z), or softmax(z)) and those scores (divided by their sum + norm_eps where
     renormalize), times route_scale; gate_out float32 [T] = sigmoid(z[:, experts]) where has_gate, else 1.  groups > 1:
     the experts are cut into `groups` runs of experts / groups consecutive indices, a run's mark is its best score plus
-    its second best, and only experts of the `keep` runs with the highest marks can be chosen."""
+    its second best, and only experts of the `keep` runs with the highest marks can be chosen.  choice_bias (float32
+    [experts]): the experts are chosen by score + choice_bias; the weights stay the scores."""
     T = z.shape[0]
+    if choice_bias is not None:
+        _req(choice_bias, "choice_bias", (torch.float32,), (experts,))
     _req(z, "z", (torch.float32,))
     _req(expert_out, "expert_out", _I32, (T, top))
     _req(weight_out, "weight_out", (torch.float32,), (T, top))
@@ -637,7 +655,22 @@ def moe_route(z, experts, top, expert_out, weight_out, gate_out=None, has_gate=F
     _check(_get("air_moe_route")(z.data_ptr(), z.shape[1], T, int(experts), int(top), 1 if score == "softmax" else 0,
                                  1 if renormalize else 0, 1 if has_gate else 0, expert_out.data_ptr(),
                                  weight_out.data_ptr(), _ptr(gate_out), int(groups), int(keep), float(route_scale),
-                                 float(norm_eps), _stream()), "moe_route")
+                                 float(norm_eps), _ptr(choice_bias), _stream()), "moe_route")
+
+
+def moe_identity(x, expert, weight, real_experts, y):
+    """The pairs (token, choice) whose expert has an index of real_experts or more are identity experts: y[choice,
+    token] = weight[token, choice] * x[token].  x [T, E]; expert int32 and weight float32 [T, top]; y float32
+    [top, T, E]."""
+    T, E = x.shape
+    top = expert.shape[1]
+    _req(x, "x", _FLOATS)
+    _req(expert, "expert", _I32, (T, top))
+    _req(weight, "weight", (torch.float32,), (T, top))
+    _req(y, "y", (torch.float32,), (top, T, E))
+    _check(_get("air_moe_identity")(x.data_ptr(), _DT[x.dtype], expert.data_ptr(), weight.data_ptr(), int(real_experts),
+                                    top, T, E, y.data_ptr(), _stream()), "moe_identity")
+    return y
 
 
 GROUP_TILE = 64      # rows of a tile of the grouped product
@@ -660,12 +693,16 @@ def moe_sort(expert, experts, start, pair_of_slot, tiles, num_tiles):
 
 def grouped_gemm(a, w, out, n, k, *, lda, ldo, groups, a_group_stride=0, o_group_stride=0, a_index=None, a_div=1,
                  a_scale=None, a_local=False, o_index=None, o_div=1, o_part_stride=0, o_local=False, start=None,
-                 rows_per_group=0, tiles=None, num_tiles=None, silu_mul=False, gate_block=0, o_scale=None, o_scale_ld=0):
+                 rows_per_group=0, tiles=None, num_tiles=None, silu_mul=False, gate_block=0, o_scale=None, o_scale_ld=0,
+                 relu2=False):
     """out rows = a rows @ w[g]^T for every group g (w [groups, n (2n with silu_mul), k]); see grouped_gemm.cu for how
     rows are found.  Strides in elements.  out is float32 or of a's type; with silu_mul out = silu(gate) * linear, the
     rows of w[g] being blocks of gate_block gate rows and as many linear rows in turn (0: all gate rows first).
     o_scale float32: the row written for slot s is multiplied, in 32-bit, by o_scale[o_index[s]], or without o_index by
-    o_scale[row * o_scale_ld + g] (row: the row of out, inside the group where o_local)."""
+    o_scale[row * o_scale_ld + g] (row: the row of out, inside the group where o_local).  relu2: out = max(product, 0)^2
+    in a's type."""
+    if relu2 and (silu_mul or out.dtype != a.dtype):
+        raise KernelError("grouped_gemm: the squared relu is written in the input's type, and is not gated")
     _req(a, "a", _FLOATS)
     _req(w, "w", (a.dtype,), (groups, 2 * n if silu_mul else n, k))
     _req(out, "out", (torch.float32, a.dtype))
@@ -684,7 +721,7 @@ def grouped_gemm(a, w, out, n, k, *, lda, ldo, groups, a_group_stride=0, o_group
         w.data_ptr(), w.shape[1] * w.shape[2], out.data_ptr(), int(ldo), int(o_group_stride), _ptr(o_index), int(o_div),
         int(o_part_stride), 1 if o_local else 0, 1 if out.dtype == torch.float32 else 0, _ptr(start),
         int(rows_per_group), _ptr(tiles), _ptr(num_tiles), tiles.shape[0] if tiles is not None else 0, int(groups),
-        int(n), int(k), _DT[a.dtype], 1 if silu_mul else 0, int(gate_block), _ptr(o_scale), int(o_scale_ld), _stream()), "grouped_gemm")
+        int(n), int(k), _DT[a.dtype], 2 if relu2 else (1 if silu_mul else 0), int(gate_block), _ptr(o_scale), int(o_scale_ld), _stream()), "grouped_gemm")
     return out
 
 
@@ -763,12 +800,13 @@ def _columns(t, name):
     return t.data_ptr(), t.stride(0)
 
 
-def short_conv_silu(x, weight, state, y, q_start, slots, max_tokens):
+def short_conv_silu(x, weight, state, y, q_start, slots, max_tokens, act=True):
     """y[t, c] = silu(sum_j weight[c, j] x[t - (taps - 1 - j), c]) for every entry of the batch (rows q_start[e] ..
     q_start[e + 1], state row slots[e]): a causal convolution over the request's tokens, whose inputs before the
     portion come from state [slots, C, taps - 1] (oldest first; zeros at a request's start) and whose last taps - 1
     inputs are left there.  x: float32 [T, C] (may be a band of columns of a wider matrix); y: float32 [T, C].
-    max_tokens: the longest portion of the batch (a host number: it sizes the grid)."""
+    max_tokens: the longest portion of the batch (a host number: it sizes the grid).  act False: the sum itself,
+    without the SiLU."""
     C, taps = weight.shape
     xp, ld = _columns(x, "x")
     _req(weight, "weight", (torch.float32,))
@@ -781,16 +819,18 @@ def short_conv_silu(x, weight, state, y, q_start, slots, max_tokens):
     if not (1 <= taps <= 16):
         raise KernelError(f"short_conv_silu: {taps} taps (the kernel takes 1 to 16)")
     _check(_get("air_short_conv_silu")(xp, ld, weight.data_ptr(), state.data_ptr(), y.data_ptr(), q_start.data_ptr(),
-                                       slots.data_ptr(), slots.shape[0], C, taps, int(max_tokens), _stream()),
+                                       slots.data_ptr(), slots.shape[0], C, taps, int(max_tokens), 1 if act else 0,
+                                       _stream()),
            "short_conv_silu")
     return y
 
 
-SCAN_DELTA, SCAN_GLA, SCAN_HGRN = 0, 1, 2
+SCAN_DELTA, SCAN_GLA, SCAN_HGRN, SCAN_RETENTION = 0, 1, 2, 3
 
 
 def linear_scan(mode, q, k, v, decay, state, out, q_start, slots, token_seq, q_scale=1.0, beta=None, a_log=None,
-                dt_bias=None, tau=1.0, unit=False, unit_eps=1e-6, lower=None, gate_bias=None):
+                dt_bias=None, tau=1.0, unit=False, unit_eps=1e-6, lower=None, gate_bias=None, positions=None, freq=None,
+                k_scale=1.0):
     """A state S [d, dv] per head and request, updated token by token in 32-bit and read out after each update.
     q, k float32 [T, G * d], v [T, H * dv] (each may be a band of columns of a wider matrix); head h reads q/k head
     h // (H / G); state [slots, H, d, dv]; out [T, H, dv]; token_seq [T]: the slot of each row's request (negative:
@@ -802,7 +842,10 @@ def linear_scan(mode, q, k, v, decay, state, out, q_start, slots, token_seq, q_s
     SCAN_GLA: decay [T, H * d] logits; alpha = sigmoid(decay)^(1 / tau); q is multiplied by q_scale;
       S = diag(alpha) S + k v^T; o = S^T q.
     SCAN_HGRN: decay [T, H * d] logits, lower and gate_bias float32 [H * d]; alpha = lower + (1 - lower) *
-      sigmoid(decay + gate_bias); k is None (k = 1 - alpha); q = silu(q) * q_scale; the recurrence is SCAN_GLA's."""
+      sigmoid(decay + gate_bias); k is None (k = 1 - alpha); q = silu(q) * q_scale; the recurrence is SCAN_GLA's.
+    SCAN_RETENTION: decay float32 [H], one constant per head; the first 2 * len(freq) elements of every head of q and k
+      are rotated (element i with i + rot / 2) by positions[t] * freq[i] (freq float64; the angle and its cos and sin
+      in 64-bit), q is multiplied by q_scale, k by k_scale; S = decay[h] S + k v^T; o = S^T q."""
     slots_n, H, d, dv = state.shape
     _req(state, "state", (torch.float32,))
     T = out.shape[0]
@@ -810,7 +853,11 @@ def linear_scan(mode, q, k, v, decay, state, out, q_start, slots, token_seq, q_s
     qp, ldq = _columns(q, "q")
     kp, ldk = _columns(k, "k") if k is not None else (None, 0)
     vp, ldv = _columns(v, "v")
-    dp, ldd = _columns(decay, "decay")
+    if mode == SCAN_RETENTION:
+        _req(decay, "decay", (torch.float32,), (H,))
+        dp, ldd = decay.data_ptr(), 0
+    else:
+        dp, ldd = _columns(decay, "decay")
     if (k is None) != (mode == SCAN_HGRN):
         raise KernelError("linear_scan: keys are given except where the gate makes them")
     if q.shape[1] % d or (k is not None and k.shape != q.shape) or v.shape[1] != H * dv:
@@ -833,6 +880,16 @@ def linear_scan(mode, q, k, v, decay, state, out, q_start, slots, token_seq, q_s
             raise KernelError("linear_scan: a forget gate per key channel of every head")
         a_log, dt_bias = _req(lower, "lower", (torch.float32,), (H * d,)), _req(gate_bias, "gate_bias",
                                                                                    (torch.float32,), (H * d,))
+    elif mode == SCAN_RETENTION:
+        if G != H:
+            raise KernelError("linear_scan: retention takes a head of q and k per head of v")
+        rot = 0
+        if freq is not None:
+            _req(freq, "freq", (torch.float64,))
+            _req(positions, "positions", _I32, (T,))
+            rot = 2 * freq.numel()
+            if rot > d:
+                raise KernelError(f"linear_scan: rotary width {rot} does not fit head size {d}")
     else:
         raise KernelError(f"linear_scan: mode {mode}")
     if d > 1024:
@@ -845,12 +902,14 @@ def linear_scan(mode, q, k, v, decay, state, out, q_start, slots, token_seq, q_s
     while lanes * rows < d:
         lanes *= 2
     kq = torch.empty((T, G, 2, lanes * rows), dtype=torch.float32, device=out.device)
-    dec = torch.empty((T, H, 2 if mode == SCAN_DELTA else lanes * rows), dtype=torch.float32, device=out.device)
+    dec = None if mode == SCAN_RETENTION else \
+        torch.empty((T, H, 2 if mode == SCAN_DELTA else lanes * rows), dtype=torch.float32, device=out.device)
     _check(_get("air_linear_scan")(
         int(mode), qp, ldq, kp, ldk, vp, ldv, dp, ldd, bp, ldb, _ptr(a_log), _ptr(dt_bias), state.data_ptr(),
-        out.data_ptr(), q_start.data_ptr(), slots.data_ptr(), token_seq.data_ptr(), kq.data_ptr(), dec.data_ptr(),
+        out.data_ptr(), q_start.data_ptr(), slots.data_ptr(), token_seq.data_ptr(), kq.data_ptr(), _ptr(dec),
         T, slots.shape[0], H, G, d, dv, lanes, float(q_scale), 1.0 / float(tau), 1 if unit else 0, float(unit_eps),
-        _stream()), "linear_scan")
+        _ptr(positions), _ptr(freq), 2 * freq.numel() if (mode == SCAN_RETENTION and freq is not None) else 0,
+        float(k_scale), _stream()), "linear_scan")
     global launches
     launches += 1
     return out
@@ -881,6 +940,50 @@ def head_gate(x, gate, token_seq):
     _check(_get("air_head_gate")(x.data_ptr(), _DT[x.dtype], gate.data_ptr(), token_seq.data_ptr(), T, H, d, _stream()),
            "head_gate")
     return x
+
+
+def sigmoid_gate(x, gate, token_seq):
+    """x[t, c] *= sigmoid(gate[t, c]) in place.  x [T, C]; gate float32 [T, C] (may be a band of columns)."""
+    T, C = x.shape
+    _req(x, "x", _FLOATS)
+    gp, ldg = _columns(gate, "gate")
+    if tuple(gate.shape) != (T, C):
+        raise KernelError("sigmoid_gate: the gate does not fit")
+    _req(token_seq, "token_seq", _I32, (T,))
+    _check(_get("air_sigmoid_gate")(x.data_ptr(), _DT[x.dtype], gp, ldg, token_seq.data_ptr(), T, C, _stream()),
+           "sigmoid_gate")
+    return x
+
+
+def relu2(x, out):
+    """out = max(x, 0)^2 element by element; x and out of one shape, float32 or bfloat16 each."""
+    _req(x, "x", _FLOATS)
+    _req(out, "out", _FLOATS, tuple(x.shape))
+    _check(_get("air_relu2")(x.data_ptr(), _DT[x.dtype], out.data_ptr(), _DT[out.dtype], x.numel(), _stream()), "relu2")
+    return out
+
+
+def normed_add_norm(h, term, term_weight, term_eps, weight, eps, out, rows=None):
+    """x = h + term / sqrt(mean(term^2) + term_eps) * term_weight, written into h when rows is None; out = x /
+    sqrt(mean(x^2) + eps) * weight.  term float32 [T, E], or [parts, T, E] partial sums that are added in order first;
+    term_weight and weight float32 [E].  With rows: out[r] is that of row rows[r], h unchanged.  weight None (and out
+    None): only the stream is completed."""
+    E = h.shape[-1]
+    _req(h, "h", (torch.float32,), (None, E))
+    parts = 1 if term.dim() == 2 else term.shape[0]
+    _req(term, "term", (torch.float32,), tuple(h.shape) if term.dim() == 2 else (parts,) + tuple(h.shape))
+    _req(term_weight, "term_weight", (torch.float32,), (E,))
+    R = h.shape[0] if rows is None else rows.shape[0]
+    if rows is not None:
+        _req(rows, "rows", _I32)
+    if weight is not None:
+        _req(weight, "weight", (torch.float32,), (E,))
+        _req(out, "out", _FLOATS, (R, E))
+    _check(_get("air_normed_add_norm")(h.data_ptr(), term.data_ptr(), parts, h.numel(), term_weight.data_ptr(),
+                                       float(term_eps), _ptr(weight), _ptr(out) if weight is not None else None,
+                                       _DT[out.dtype] if weight is not None else 0, _ptr(rows), R, E, float(eps),
+                                       _stream()), "normed_add_norm")
+    return out
 
 
 def glu(gate_up, out, block=None, alpha=1.0, limit=0.0, shift=0.0):

@@ -4,7 +4,8 @@
 // padding, skipped).  Everything here is 32-bit: inputs, states and arithmetic.
 //
 //   short_conv_silu_kernel   y[t, c] = silu(sum_j w[c, j] x[t - (taps - 1 - j), c]): a causal convolution over time
-//                            per channel whose last taps - 1 inputs are the state (zeros before a request's start)
+//                            per channel whose last taps - 1 inputs are the state (zeros before a request's start);
+//                            with act 0 the sum itself, without the SiLU
 //   scan_prepare_kernel      what a scan reads per token (unit lengths, scales, decays), for all tokens side by side
 //   linear_scan_kernel       a state S [d, dv] per head, updated token by token, read out after each update:
 //                              DELTA  S = g S;  u = beta (v - S^T k);  S += k u^T;  o = S^T q   (one decay per head)
@@ -12,6 +13,8 @@
 //                              HGRN   the same recurrence with k = 1 - alpha (the complement of the decay stands where
 //                                     a key would); alpha = l + (1 - l) sigmoid(z + bias) with a lower bound l per
 //                                     channel, q = silu(q)
+//                              RET    S = g_h S + k v^T;  o = S^T q with one constant g_h per head (retention); q and k
+//                                     are first rotated by the token's position, k then multiplied by a constant
 //                            Columns of S do not depend on one another, so a block takes a few of them and a column is
 //                            held in the registers of L lanes of one warp; the tokens of a portion are taken in order.
 //                            What a token's output is depends on the state and the tokens before it only, not on how
@@ -34,7 +37,7 @@ __device__ __forceinline__ float log_sigmoid_f(float x) { return fminf(x, 0.f) -
 __global__ void __launch_bounds__(CONV_THREADS)
 short_conv_silu_kernel(const float* __restrict__ x, int ld, const float* __restrict__ w, float* __restrict__ state,
                        float* __restrict__ y, const int* __restrict__ q_start, const int* __restrict__ slots,
-                       int C, int taps, int chunk) {
+                       int C, int taps, int chunk, int act) {
     pdl_enter(TR_CONV);
     const int c = blockIdx.x * CONV_THREADS + threadIdx.x;
     const int e = blockIdx.y;
@@ -68,7 +71,7 @@ short_conv_silu_kernel(const float* __restrict__ x, int ld, const float* __restr
 #pragma unroll
         for (int j = 0; j < M - 1; ++j)
             if (j >= lead) acc = fmaf(wv[j], win[j], acc);
-        y[(size_t)(q0 + t) * C + c] = silu_f(acc);
+        y[(size_t)(q0 + t) * C + c] = act ? silu_f(acc) : acc;
 #pragma unroll
         for (int j = 0; j < M - 2; ++j) win[j] = win[j + 1];
         win[M - 2] = cur;
@@ -84,7 +87,7 @@ short_conv_silu_kernel(const float* __restrict__ x, int ld, const float* __restr
     }
 }
 
-enum { SCAN_DELTA = 0, SCAN_GLA = 1, SCAN_HGRN = 2 };
+enum { SCAN_DELTA = 0, SCAN_GLA = 1, SCAN_HGRN = 2, SCAN_RET = 3 };
 constexpr int SCAN_THREADS = 128;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -105,6 +108,10 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 //                        GLA   [T, H, dpad]: alpha = sigmoid(decay)^(1 / tau) per key channel, zeros from d on
 //                        HGRN  [T, H, dpad]: alpha = l + (1 - l) sigmoid(decay + bias); kq's k is 1 - alpha (no k is
 //                              read) and its q is silu(q) * q_scale
+//                        RET   nothing: the decay is one constant per head, read by the scan from decay [H]; kq's q and
+//                              k have their first `rot` elements rotated (element i with i + rot / 2, angle position *
+//                              freq[i] as a 64-bit product, its cos and sin taken in 64-bit), q times q_scale, k times
+//                              k_scale
 struct ScanPrepArgs {
     const float* q; int ldq;         // [T, ldq]: head g's d elements at column g * d
     const float* k; int ldk;
@@ -118,6 +125,10 @@ struct ScanPrepArgs {
     int H, G, d, dpad;
     float q_scale, inv_tau, unit_eps;
     int unit;                        // q and k are divided by sqrt(sum of squares + unit_eps) first
+    const int* positions;            // RET: [T]
+    const double* freq;              // RET: [rot / 2]
+    int rot;
+    float k_scale;
 };
 
 template <int MODE>
@@ -146,6 +157,31 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(const ScanPrepArgs p)
         return;
     }
     const float* kin = p.k + (size_t)t * p.ldk + g * p.d;
+    if (MODE == SCAN_RET) {
+        float* out = p.kq + ((size_t)t * p.G + g) * 2 * p.dpad;
+        const int half = p.rot / 2;
+        const double pos = (double)p.positions[t];
+        for (int r = threadIdx.x; r < p.dpad; r += blockDim.x) {
+            float k = 0.f, q = 0.f;
+            if (r < p.d) {
+                k = kin[r];
+                q = qin[r];
+                if (r < p.rot) {
+                    const int j = r < half ? r : r - half;
+                    double sn, cs;
+                    sincos(pos * p.freq[j], &sn, &cs);
+                    const float c = (float)cs, s = (float)sn;
+                    const int other = r < half ? r + half : r - half;
+                    // (a, b) -> (a c - b s, b c + a s): the first of a pair subtracts, the second adds
+                    k = r < half ? k * c - kin[other] * s : k * c + kin[other] * s;
+                    q = r < half ? q * c - qin[other] * s : q * c + qin[other] * s;
+                }
+            }
+            out[r] = k * p.k_scale;
+            out[p.dpad + r] = q * p.q_scale;
+        }
+        return;
+    }
     float kf = 1.f, qf = p.q_scale;
     if (p.unit) {
         float sk = 0.f, sq = 0.f;
@@ -210,7 +246,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
     const int g = h / (p.H / p.G);
 
     // a buffer: kq [TK][2][dpad], then (GLA) alpha [TK][dpad] or (DELTA) g, b [TK][2], then v [TK][CB]
-    const int dec_floats = MODE == SCAN_GLA ? TK * dpad : ((2 * TK + 3) & ~3);
+    const int dec_floats = MODE == SCAN_GLA ? TK * dpad : (MODE == SCAN_RET ? 0 : ((2 * TK + 3) & ~3));
     const int buf_floats = TK * 2 * dpad + dec_floats + TK * CB;
     float* so = smem + 2 * buf_floats;                           // [TK][CB][L]: the lanes' partial read-outs
 
@@ -230,7 +266,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
                 const int tt = idx / per, c = idx % per;
                 cp_async16(bdec + tt * dpad + 4 * c, p.dec + ((size_t)(q0 + t0 + tt) * p.H + h) * dpad + 4 * c);
             }
-        } else {
+        } else if (MODE == SCAN_DELTA) {
             for (int idx = threadIdx.x; idx < cnt * 2; idx += SCAN_THREADS)
                 cp_async4(bdec + idx, p.dec + ((size_t)(q0 + t0 + idx / 2) * p.H + h) * 2 + (idx & 1));
         }
@@ -242,6 +278,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
     };
 
     stage(0, 0);
+    const float ghead = MODE == SCAN_RET ? p.dec[h] : 0.f;      // the head's constant decay
     float S[R];
     float* st = p.state + ((size_t)slot * p.H + h) * p.d * p.dv;
 #pragma unroll
@@ -281,6 +318,12 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
 #pragma unroll
                 for (int i = 0; i < R; ++i) {
                     S[i] = fmaf(kr[i], u, S[i]);
+                    orr[i & 3] = fmaf(S[i], qq[i * L], orr[i & 3]);
+                }
+            } else if (MODE == SCAN_RET) {
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    S[i] = fmaf(ghead, S[i], kk[i * L] * vv);
                     orr[i & 3] = fmaf(S[i], qq[i * L], orr[i & 3]);
                 }
             } else {
@@ -367,7 +410,7 @@ static int launch_scan(const ScanPrepArgs& prep, const ScanArgs& a, int T, int S
     const int CB = SCAN_THREADS / L;
     // two buffers of `tokens` tokens each, and their partial read-outs, within 96 KB
     auto bytes = [&](int tk) {
-        const size_t dec = MODE == SCAN_GLA ? (size_t)tk * dpad : (size_t)((2 * tk + 3) & ~3);
+        const size_t dec = MODE == SCAN_GLA ? (size_t)tk * dpad : (MODE == SCAN_RET ? 0 : (size_t)((2 * tk + 3) & ~3));
         return sizeof(float) * (2 * ((size_t)tk * 2 * dpad + dec + (size_t)tk * CB) + (size_t)tk * SCAN_THREADS);
     };
     int tk = 16;
@@ -412,7 +455,8 @@ static int launch_scan(const ScanPrepArgs& prep, const ScanArgs& a, int T, int S
 }  // namespace air
 
 AIR_API int air_short_conv_silu(const float* x, int ld, const float* w, float* state, float* y, const int* q_start,
-                                const int* slots, int S, int C, int taps, int max_tokens, cudaStream_t stream) {
+                                const int* slots, int S, int C, int taps, int max_tokens, int act,
+                                cudaStream_t stream) {
     if (S <= 0 || C <= 0) return 0;
     if (taps < 1 || taps > air::CONV_MAX_TAPS || S > 65535) return AIR_ERR_BAD_ARGUMENT;
     const int chunk = 64;
@@ -421,24 +465,27 @@ AIR_API int air_short_conv_silu(const float* x, int ld, const float* w, float* s
     if (chunks > 65535) return AIR_ERR_BAD_ARGUMENT;
     dim3 grid((C + air::CONV_THREADS - 1) / air::CONV_THREADS, S, chunks);
     return air::launch(air::short_conv_silu_kernel, grid, air::CONV_THREADS, 0, stream, x, ld, w, state, y, q_start,
-                       slots, C, taps, chunk);
+                       slots, C, taps, chunk, act);
 }
 
 // kq: float32 workspace [T, G, 2, L * R] and dec: [T, H, 2] (mode 0) or [T, H, L * R] (modes 1, 2), with R = 16 up to
-// 512 key channels and 32 beyond, L the power of two with L * R >= d.
+// 512 key channels and 32 beyond, L the power of two with L * R >= d.  Mode 3 (retention): decay is [H], the heads'
+// constants, and no dec is needed; positions [T], freq float64 [rot / 2], k_scale as ScanPrepArgs says.
 AIR_API int air_linear_scan(int mode, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
                             const float* decay, int ldd, const float* beta, int ldb, const float* a_log,
                             const float* dt_bias, float* state, float* out, const int* q_start, const int* slots,
                             const int* token_seq, float* kq, float* dec, int T, int S, int H, int G, int d, int dv,
-                            int L, float q_scale, float inv_tau, int unit, float unit_eps, cudaStream_t stream) {
+                            int L, float q_scale, float inv_tau, int unit, float unit_eps, const int* positions,
+                            const double* freq, int rot, float k_scale, cudaStream_t stream) {
     if (S <= 0 || T <= 0) return 0;
-    if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || !kq || !dec || ((uintptr_t)kq & 15) || ((uintptr_t)dec & 15))
+    if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || !kq || ((uintptr_t)kq & 15) ||
+        (mode != air::SCAN_RET && (!dec || ((uintptr_t)dec & 15))))
         return AIR_ERR_BAD_ARGUMENT;
     air::ScanPrepArgs pr;
     pr.q = q; pr.ldq = ldq; pr.k = k; pr.ldk = ldk; pr.decay = decay; pr.ldd = ldd; pr.beta = beta; pr.ldb = ldb;
     pr.a_log = a_log; pr.dt_bias = dt_bias; pr.token_seq = token_seq; pr.kq = kq; pr.dec = dec; pr.H = H; pr.G = G;
     pr.d = d; pr.dpad = L * air::scan_rows(d); pr.q_scale = q_scale; pr.inv_tau = inv_tau; pr.unit_eps = unit_eps;
-    pr.unit = unit;
+    pr.unit = unit; pr.positions = positions; pr.freq = freq; pr.rot = rot; pr.k_scale = k_scale;
     air::ScanArgs a;
     a.kq = kq; a.dec = dec; a.v = v; a.ldv = ldv; a.state = state; a.out = out; a.q_start = q_start; a.slots = slots;
     a.H = H; a.G = G; a.d = d; a.dv = dv; a.L = L; a.tokens = 0;
@@ -447,6 +494,12 @@ AIR_API int air_linear_scan(int mode, const float* q, int ldq, const float* k, i
     if (mode == air::SCAN_HGRN) {
         if (G != H || !a_log || !dt_bias) return AIR_ERR_BAD_ARGUMENT;
         return air::launch_scan<air::SCAN_HGRN>(pr, a, T, S, stream);
+    }
+    if (mode == air::SCAN_RET) {
+        if (G != H || !decay || rot < 0 || rot > d || (rot & 1) || (rot && (!positions || !freq)))
+            return AIR_ERR_BAD_ARGUMENT;
+        a.dec = decay;
+        return air::launch_scan<air::SCAN_RET>(pr, a, T, S, stream);
     }
     return AIR_ERR_BAD_ARGUMENT;
 }

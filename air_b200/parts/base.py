@@ -246,6 +246,17 @@ class GatedSum:
     gate: Optional[torch.Tensor]
 
 
+@dataclass
+class NormedSum:
+    """What a sub-layer with a norm BEHIND it adds to the stream: term / sqrt(mean(term^2) + eps) * weight, with term
+    float32 [T, hidden] or [parts, T, hidden] partial sums (added in order first) and weight float32 [hidden].  A form
+    of a norm's `delta`: the norm that follows takes the norm of the term, completes the stream with it and normalises
+    the stream in one kernel."""
+    term: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+
+
 class Part:
     # True if forward() only launches work on the current stream from device data (no host
     # reads of the batch or of a result), so that a decode step can be captured in a CUDA graph.
@@ -288,6 +299,8 @@ class Norm(Part):
                 ops.scaled_norm(h, delta.terms, None, 0.0, None)
             elif isinstance(delta, GatedSum):
                 ops.post_norm(h, 1.0, delta.a, delta.b, delta.gate, None, 0.0, None)
+            elif isinstance(delta, NormedSum):
+                ops.normed_add_norm(h, delta.term, delta.weight, delta.eps, None, 0.0, None)
             else:
                 ops.add_parts(h, delta)
         return h

@@ -121,6 +121,70 @@ class PreNormBlock(Block):
         return h, self._scaled(self.feed_forward.forward(x, ctx))
 
 
+@register_block("sandwich")
+class SandwichBlock(Block):
+    """h = h + norm_b(mixer(norm_a(h))); h = h + norm_d(feed_forward(norm_c(h))): a norm on each side of every
+    sub-layer.  Roles: mixer_norm, mixer, mixer_out_norm, and feed_forward_norm, feed_forward, feed_forward_out_norm (a
+    layer may lack the last three).  The norms in front are of a registered kind; the norms behind are weights [hidden]
+    named by the roles mixer_out_norm and feed_forward_out_norm (x / sqrt(mean(x^2) + eps) * w with the eps of the parts
+    of those roles).
+
+    A sub-layer's output is handed on as a NormedSum, so that ONE kernel takes its norm, adds it to the float32 stream
+    and takes the norm in front of the next sub-layer (of this block, of the next one, or the model's last one).  The
+    parameter idle lists (what follows the prefix, shape) of tensors that a model file may hold for the layer although
+    the layer does not use them."""
+
+    def __init__(self, spec: BlockSpec):
+        super().__init__(spec)
+        self.mixer_norm = NORMS.get(spec.part("mixer_norm").kind)(spec.part("mixer_norm"), spec.name("mixer_norm"))
+        self.mixer = MIXERS.get(spec.part("mixer").kind)(spec.part("mixer"), spec.name("mixer"))
+        self.mixer_out = NORMS.get(spec.part("mixer_out_norm").kind)(spec.part("mixer_out_norm"),
+                                                                     spec.name("mixer_out_norm"))
+        self.ff_norm = self.feed_forward = self.ff_out = None
+        if "feed_forward" in spec.parts:
+            self.ff_norm = NORMS.get(spec.part("feed_forward_norm").kind)(spec.part("feed_forward_norm"),
+                                                                          spec.name("feed_forward_norm"))
+            self.feed_forward = FEED_FORWARDS.get(spec.part("feed_forward").kind)(spec.part("feed_forward"),
+                                                                                  spec.name("feed_forward"))
+            self.ff_out = NORMS.get(spec.part("feed_forward_out_norm").kind)(spec.part("feed_forward_out_norm"),
+                                                                             spec.name("feed_forward_out_norm"))
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_out, self.ff_norm, self.feed_forward,
+                                 self.ff_out) if p is not None)
+
+    def tensor_specs(self):
+        from ..weights.loader import TensorSpec
+        return super().tensor_specs() + [TensorSpec(self.spec.prefix + name, tuple(shape), optional=True, wide=True)
+                                         for name, shape in self.spec.params.get("idle", ())]
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    @staticmethod
+    def _behind(norm, delta):
+        """What a sub-layer returned, as the sum that the next norm adds: its norm with the weight of `norm`."""
+        import torch
+        from ..csrc import ops
+        from .base import GatedSum, NormedSum, ScaledSum
+        if isinstance(delta, (GatedSum, ScaledSum, NormedSum)) or delta is None:
+            raise ops.KernelError("sandwich: the sub-layer must return its output as a tensor or as partial sums")
+        if delta.dtype != torch.float32:
+            delta = ops.convert(delta, torch.empty(delta.shape, dtype=torch.float32, device=delta.device))
+        w = norm.weight if norm.weight.dtype == torch.float32 else norm.weight.to(torch.float32)
+        norm.weight = w
+        return NormedSum(delta, w, norm.eps)
+
+    def forward(self, h, pending, ctx, cache, owns_cache=True):
+        ctx.residual = None          # a sub-layer's output is normalised before it is added: the parts return it
+        x = self.mixer_norm.forward(h, pending)
+        a = self._behind(self.mixer_out, self.mixer.forward(x, ctx, cache, owns_cache))
+        if self.feed_forward is None:
+            return h, a
+        x = self.ff_norm.forward(h, a)
+        return h, self._behind(self.ff_out, self.feed_forward.forward(x, ctx))
+
+
 @register_block("parallel")
 class ParallelBlock(Block):
     """x = norm(h); h = h + s_m * mixer(x) + s_f * feed_forward(x): one norm whose rows both sub-layers read, their

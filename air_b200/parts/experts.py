@@ -33,10 +33,16 @@ class RoutedExperts(FeedForward):
     (Wup u)).  The shared expert (shared_intermediate > 0) has the same form and runs for every token; with shared_gate
     its output is multiplied by g = sigmoid(w_sg . x), one number per token, else g = 1.
 
+    With gated False an expert has no gate: expert(u) = Wdown act(Wup u) with act the square of the rectifier
+    (activation "relu2").  With choice_bias the experts are chosen by score + bias (a learned number per expert, the
+    tensor `correction`) while the weights stay the scores.  With identity = n the router has n more outputs behind the
+    experts' own; they stand for experts without matrices whose output is their input (times the weight), and they
+    take part in the softmax and in the choice like the others.
+
     params: hidden, experts, top, intermediate, shared_intermediate, shared_gate, score, renormalize, norm_eps,
-    route_scale, groups, weight_on.
-    Tensors: <prefix>router [experts, hidden], e<i>.gate, e<i>.up [intermediate, hidden], e<i>.down [hidden,
-    intermediate], shared.gate, shared.up, shared.down, shared.sg [1, hidden].
+    route_scale, groups, weight_on, gated, activation, choice_bias, identity.
+    Tensors: <prefix>router [experts + identity, hidden], e<i>.gate, e<i>.up [intermediate, hidden], e<i>.down [hidden,
+    intermediate], shared.gate, shared.up, shared.down, shared.sg [1, hidden], correction [experts + identity].
 
     Everything happens on the device: a kernel picks the experts, one orders the (token, choice) pairs by expert, and
     two grouped products (gate and up with the activation; down) walk the experts' rows.  The outputs of a token's
@@ -65,7 +71,18 @@ class RoutedExperts(FeedForward):
                                 or self.top > self.keep * (self.experts // self.groups)):
             raise ConfigError("data_error", "routed experts: the groups must be equal, keep between 1 and their number, "
                                             "and the kept groups must hold at least `top` experts")
-        if self.experts > 512 or self.top > 32:
+        self.gated, self.activation = bool(p.get("gated", True)), p.get("activation", "silu")
+        self.choice_bias, self.identity = bool(p.get("choice_bias", False)), int(p.get("identity") or 0)
+        self.outputs = self.experts + self.identity          # what the router chooses among
+        if (self.gated, self.activation) not in ((True, "silu"), (False, "relu2")):
+            raise ConfigError("unsupported", "routed experts: gated experts with SiLU, or plain ones with the squared "
+                                             "rectifier")
+        if self.identity < 0 or (self.identity and (self.weight_on != "output" or self.groups > 1)):
+            raise ConfigError("unsupported", "routed experts: identity experts take their weight on the output, and "
+                                             "no groups")
+        if self.top > self.outputs:
+            raise ConfigError("data_error", "routed experts: more choices than experts")
+        if self.outputs > 512 or self.top > 32:
             raise ConfigError("unsupported", "routed experts: up to 512 experts and 32 choices per token")
         self.shared = None
         if self.shared_inter:
@@ -75,10 +92,12 @@ class RoutedExperts(FeedForward):
 
     def tensor_specs(self):
         p, e, f = self.prefix, self.hidden, self.inter
-        specs = [TensorSpec(p + "router", (self.experts, e), wide=True)]
+        specs = [TensorSpec(p + "router", (self.outputs, e), wide=True)]
+        if self.choice_bias:
+            specs.append(TensorSpec(p + "correction", (self.outputs,), wide=True, std=0.01))
         for i in range(self.experts):
-            specs += [TensorSpec(f"{p}e{i}.gate", (f, e)), TensorSpec(f"{p}e{i}.up", (f, e)),
-                      TensorSpec(f"{p}e{i}.down", (e, f))]
+            specs += ([TensorSpec(f"{p}e{i}.gate", (f, e))] if self.gated else []) + \
+                [TensorSpec(f"{p}e{i}.up", (f, e)), TensorSpec(f"{p}e{i}.down", (e, f))]
         if self.shared is not None:
             specs += self.shared.tensor_specs()
         if self.shared_gate:
@@ -108,8 +127,12 @@ class RoutedExperts(FeedForward):
                 return torch.cat([g, u], dim=0)
             return torch.stack([g.view(F // block, block, -1), u.view(F // block, block, -1)], dim=1).reshape(2 * F, -1)
 
-        self.gate_up = torch.stack([arranged(tensors[f"{p}e{i}.gate"], tensors[f"{p}e{i}.up"])
-                                    for i in range(n)]).contiguous()             # [n, 2F, E]
+        if self.gated:
+            self.gate_up = torch.stack([arranged(tensors[f"{p}e{i}.gate"], tensors[f"{p}e{i}.up"])
+                                        for i in range(n)]).contiguous()             # [n, 2F, E]
+        else:
+            self.gate_up = torch.stack([tensors[f"{p}e{i}.up"] for i in range(n)]).contiguous()      # [n, F, E]
+        self.correction = tensors[p + "correction"].to(torch.float32).contiguous() if self.choice_bias else None
         self.down = torch.stack([tensors[f"{p}e{i}.down"] for i in range(n)]).contiguous()      # [n, E, F]
         if self.gate_up.dtype != rt.dtype:
             raise ValueError(f"{p}: the experts are stored as {self.gate_up.dtype}, the engine computes in {rt.dtype}")
@@ -123,9 +146,9 @@ class RoutedExperts(FeedForward):
         expert = torch.empty((T, top), dtype=torch.int32, device=dev)
         weight = torch.empty((T, top), dtype=torch.float32, device=dev)
         gate = torch.empty((T,), dtype=torch.float32, device=dev) if self.shared_gate else None
-        ops.moe_route(z, n, top, expert, weight, gate, has_gate=self.shared_gate, score=self.score,
+        ops.moe_route(z, self.outputs, top, expert, weight, gate, has_gate=self.shared_gate, score=self.score,
                       renormalize=self.renormalize, groups=self.groups, keep=self.keep, route_scale=self.route_scale,
-                      norm_eps=self.norm_eps)
+                      norm_eps=self.norm_eps, choice_bias=self.correction)
         on_input = self.weight_on == "input"
         pairs = T * top
         ints = torch.empty(n + 1 + pairs + 2 * (pairs // ops.GROUP_TILE + n) + 1, dtype=torch.int32, device=dev)
@@ -133,13 +156,17 @@ class RoutedExperts(FeedForward):
         tiles, num_tiles = ints[n + 1 + pairs:-1].view(-1, 2), ints[-1:]
         ops.moe_sort(expert, n, start, pair_of_slot, tiles, num_tiles)
         y = torch.empty((top, T, E), dtype=torch.float32, device=dev)
+        if self.identity:
+            # (pairs of an expert without matrices get no slot in the order by expert: their planes are written here)
+            ops.moe_identity(x, expert, weight, n, y)
         if x.dtype == torch.bfloat16 and pairs >= self.LIBRARY_ROWS * n and E % 16 == 0 and F % 16 == 0:
             self._experts_by_the_library(x, start, pair_of_slot, weight, y)
         else:
             act = torch.empty((pairs, F), dtype=x.dtype, device=dev)
             ops.grouped_gemm(x, self.gate_up, act, F, E, lda=E, ldo=F, groups=n, a_index=pair_of_slot, a_div=top,
                              a_scale=weight.view(-1) if on_input else None, start=start, tiles=tiles,
-                             num_tiles=num_tiles, silu_mul=True, gate_block=self.block)
+                             num_tiles=num_tiles, silu_mul=self.gated, gate_block=self.block if self.gated else 0,
+                             relu2=not self.gated)
             ops.grouped_gemm(act, self.down, y, E, F, lda=F, ldo=E, groups=n, o_index=pair_of_slot, o_div=top,
                              o_part_stride=T * E, start=start, tiles=tiles, num_tiles=num_tiles,
                              o_scale=None if on_input else weight.view(-1))
@@ -158,6 +185,10 @@ class RoutedExperts(FeedForward):
                                  torch.empty((pairs, E), dtype=x.dtype, device=x.device))
         ends = start[1:].clone()
         act = torch.empty((pairs, self.inter), dtype=x.dtype, device=x.device)
-        ops.silu_mul(torch._grouped_mm(rows, self.gate_up.transpose(1, 2), offs=ends), act, block=self.block)
+        hidden = torch._grouped_mm(rows, self.gate_up.transpose(1, 2), offs=ends)
+        if self.gated:
+            ops.silu_mul(hidden, act, block=self.block)
+        else:
+            ops.relu2(hidden, act)
         ops.planes_by_index(torch._grouped_mm(act, self.down.transpose(1, 2), offs=ends), pair_of_slot, top, y,
                             scale=None if on_input else weight.view(-1))

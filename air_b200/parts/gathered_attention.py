@@ -21,7 +21,8 @@ class PortionAttention:
     which a block serves all query heads of a key/value head (ops.grouped_attention), or, for sizes that are not whole
     16-byte pieces, the one with a block per head.
 
-    The mixer offers: rt, heads, kv_heads (1 for a latent), scale, window, chunk, and sinks (float32 [heads] or None)."""
+    The mixer offers: rt, heads, kv_heads (1 for a latent), scale, window, chunk, sinks (float32 [heads] or None) and
+    optionally softcap (> 0: a score s becomes softcap * tanh(s / softcap))."""
 
     PORTION = 32
     BLOCK = 1024
@@ -55,6 +56,7 @@ class PortionAttention:
     def attend(self, q, cache, bt, ctx, out, *, latent=False, kv_heads=1, page_tokens=None):
         """out [T, H, dv] = attention of q [T, H, dk] (float32, or the cache's type) over the request's pages."""
         sinks = getattr(self, "sinks", None)
+        softcap = float(getattr(self, "softcap", 0.0) or 0.0)
         plan = ctx.plans.get((self.PLAN,)) if not self.rt.is_fp32 else None
 
         def through_the_pages(token_seq):
@@ -62,7 +64,7 @@ class PortionAttention:
             kernel = ops.grouped_attention if ops.grouped_attention_ok(cache.dtype, q.shape[2], out.shape[2]) \
                 else ops.paged_attention_ref
             kernel(q, cache, bt, token_seq, ctx.positions, out, self.window, self.scale, kv_heads=kv_heads,
-                   page_tokens=page_tokens, chunk=self.chunk, sink=sinks, latent=latent)
+                   page_tokens=page_tokens, chunk=self.chunk, sink=sinks, latent=latent, softcap=softcap)
 
         if plan is None or not plan.portions:
             through_the_pages(ctx.token_seq)
@@ -94,7 +96,7 @@ class PortionAttention:
                     torch.mm(rows[g], keys[g].t(), out_dtype=torch.float32, out=scores[g])
                 weights = torch.empty(scores.shape, dtype=torch.bfloat16, device=dev)
                 ops.masked_softmax(scores, weights, J, lo, L, p0, self.scale, window=self.window, chunk=self.chunk,
-                                   sink=sinks)
+                                   sink=sinks, softcap=softcap)
                 summed = torch.empty((G, nb * J, dv), dtype=torch.bfloat16, device=dev)
                 for g in range(G):
                     torch.mm(weights[g], keys[g, :, :dv] if latent else values[g], out=summed[g])

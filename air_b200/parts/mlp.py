@@ -164,3 +164,34 @@ class PolyNormMLP(FeedForward):
         act = torch.empty((x.shape[0], self.padded), dtype=self.rt.dtype, device=x.device)
         ops.polynorm(z, self.up_bias, self.coefficients, self.eps, act, self.intermediate)
         return self.down.f32_sums(act)
+
+
+@register_feed_forward("relu2_mlp")
+class Relu2MLP(FeedForward):
+    """down(max(up(x), 0)^2): one hidden layer without a gate and without biases, whose activation is the square of
+    the rectifier.  params: hidden, intermediate.  Tensors: <prefix>up [intermediate, hidden], down [hidden,
+    intermediate].
+
+    The hidden layer leaves the first product in 32-bit where the step has few rows (the tcgen05 product for few rows)
+    or the engine is float32, else in the compute dtype; one kernel squares the rectified values and writes them in the
+    compute dtype."""
+
+    graph_safe = True
+
+    def tensor_specs(self):
+        e, f, p = self.spec["hidden"], self.spec["intermediate"], self.prefix
+        return [TensorSpec(p + "up", (f, e)), TensorSpec(p + "down", (e, f))]
+
+    def load(self, tensors, rt):
+        super().load(tensors, rt)
+        self.intermediate = self.spec["intermediate"]
+        self.up = Linear(tensors[self.prefix + "up"], rt.status)
+        self.down = Linear(tensors[self.prefix + "down"], rt.status)
+
+    def forward(self, x, ctx):
+        if self.rt.is_fp32 or self.up.small(x):
+            z = self.up.f32(x)
+        else:
+            z = self.up(x, self.rt.dtype)
+        act = ops.relu2(z, torch.empty(z.shape, dtype=self.rt.dtype, device=x.device))
+        return self.down.f32_sums(act)

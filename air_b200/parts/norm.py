@@ -5,7 +5,7 @@ import torch
 
 from ..csrc import ops
 from ..weights.loader import TensorSpec
-from .base import GatedSum, Norm, PreNormed, ScaledSum
+from .base import GatedSum, Norm, NormedSum, PreNormed, ScaledSum
 from .registry import register_norm
 
 
@@ -46,6 +46,12 @@ class RMSNorm(Norm):
                 raise ops.KernelError("rms: a sum with a gate per row for chosen rows is not offered")
             self.add_delta(h, delta)
             delta = None
+        if isinstance(delta, NormedSum):
+            # a sub-layer's output with a norm of its own behind it: one kernel takes that norm, completes the stream
+            # and normalises it
+            if self.weight.dtype != torch.float32:
+                self.weight = self.weight.to(torch.float32)
+            return ops.normed_add_norm(h, delta.term, delta.weight, delta.eps, self.weight, self.eps, out, rows=rows)
         if isinstance(delta, ScaledSum):
             # the outputs of sub-layers that stand side by side, each with its scale per column: one kernel
             # completes the stream with them and normalises
@@ -56,7 +62,7 @@ class RMSNorm(Norm):
         """As forward() without rows, for a part that takes its input as PreNormed: the stream is completed and
         the rows are written short of their scale, by many small blocks that do not wait for one another."""
         T, E = h.shape
-        if isinstance(delta, (ScaledSum, GatedSum)):
+        if isinstance(delta, (ScaledSum, GatedSum, NormedSum)):
             self.add_delta(h, delta)
             delta = None
         xg = torch.empty((T, E), dtype=torch.bfloat16, device=h.device)

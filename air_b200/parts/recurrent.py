@@ -220,3 +220,69 @@ class HGRN2(_StateMixer):
         y = torch.empty((T, H * dv), dtype=self.rt.dtype, device=o.device)
         ops.gated_rmsnorm(o, None, self.norm_weight, self.eps, y, ctx.token_seq)
         return self.o.f32_sums(y)
+
+
+@register_mixer("retention")
+class Retention(_StateMixer):
+    """Retention: linear attention with one constant decay per head and neither softmax nor denominator.  q = W_q x,
+    k = W_k x (heads x head_dim), v = W_v x (heads x v_dim); q and k are rotated by the token's position (the position
+    encoding's frequencies, the first part of a head), k is then multiplied by head_dim^-1/2; per head and token
+
+        S = g_h S + k v^T;   o = S^T q
+
+    with g_h the head's entry of `decay`; then each head's o over its root mean square (o / sqrt(mean(o^2) + eps), no
+    weight), times silu(W_g x), and the output projection.  S is the request's state, 32-bit, zero at its start.  The
+    rotation, the state and the norm are 32-bit.
+
+    params: hidden, heads, head_dim, v_dim, decay (a number per head), eps, position (a position encoding that gives
+    64-bit frequencies, or none).  Tensors: <prefix>q, k [heads*head_dim, hidden]; v, g [heads*v_dim, hidden];
+    o [hidden, heads*v_dim]."""
+
+    def __init__(self, spec, prefix=""):
+        super().__init__(spec, prefix)
+        from .registry import POSITION_ENCODINGS
+        p = spec.params
+        self.hidden, self.heads, self.head_dim, self.v_dim = p["hidden"], p["heads"], p["head_dim"], p["v_dim"]
+        self.eps = float(p["eps"])
+        self.decay = tuple(float(g) for g in p["decay"])
+        if len(self.decay) != self.heads:
+            raise ConfigError("data_error", f"retention: {len(self.decay)} decays for {self.heads} heads")
+        if self.head_dim > 1024:
+            raise ConfigError("unsupported", f"retention: {self.head_dim} key channels per head (up to 1,024)")
+        pos = p.get("position")
+        self.position = POSITION_ENCODINGS.get(pos.kind)(pos) if pos is not None else None
+
+    def cache_needs(self):
+        return (SlotState((self.heads, self.head_dim, self.v_dim)),)
+
+    def tensor_specs(self):
+        p, e, H, d, dv = self.prefix, self.hidden, self.heads, self.head_dim, self.v_dim
+        return [TensorSpec(p + "q", (H * d, e)), TensorSpec(p + "k", (H * d, e)), TensorSpec(p + "v", (H * dv, e)),
+                TensorSpec(p + "g", (H * dv, e)), TensorSpec(p + "o", (e, H * dv))]
+
+    def load(self, tensors, rt):
+        super().load(tensors, rt)
+        self._project(tensors, ["q", "k", "v", "g"], rt)
+        self.o = Linear(tensors[self.prefix + "o"], rt.status)
+        self.decays = torch.tensor(self.decay, dtype=torch.float32, device=rt.device)
+        self.norm_weight = torch.ones(self.v_dim, dtype=torch.float32, device=rt.device)
+        self.freq = None
+        if self.position is not None:
+            self.position.load(tensors, rt)
+            if self.position.rotary_dim:
+                if not hasattr(self.position, "frequencies64") or getattr(self.position, "pairing", "half") != "half" \
+                        or getattr(self.position, "magnitude", 1.0) != 1.0:
+                    raise ConfigError("unsupported", "retention takes a half-split rotation with 64-bit frequencies")
+                if self.position.rotary_dim > self.head_dim:
+                    raise ConfigError("data_error", "retention: the rotated part is larger than a head")
+                self.freq = self.position.frequencies64()
+
+    def forward(self, x, ctx, cache, owns_cache=True):
+        (state,) = cache
+        T, H, d, dv = x.shape[0], self.heads, self.head_dim, self.v_dim
+        proj = self.proj.f32(x)
+        o = torch.empty((T, H, dv), dtype=torch.float32, device=x.device)
+        ops.linear_scan(ops.SCAN_RETENTION, self._band(proj, "q"), self._band(proj, "k"), self._band(proj, "v"),
+                        self.decays, state.state, o, ctx.q_start, ctx.slots, ctx.token_seq, positions=ctx.positions,
+                        freq=self.freq, k_scale=d ** -0.5)
+        return self._finish(o, proj, ctx)

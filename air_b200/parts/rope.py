@@ -91,12 +91,32 @@ def bent_frequencies(rot: int, theta: float, scaling=None):
     return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
 
 
+def banded_frequencies(rot: int, theta: float, scaling=None):
+    """float64 frequencies [rot / 2] of a rotation whose slow pairs are slowed down by a constant factor, the fast ones
+    left alone and the band between them blended (the rule of Llama 3.1).  scaling: None, or a mapping with factor,
+    original (the trained length), low and high.  With the wavelength l_i = 2 pi / f_i: f_i stays where l_i <
+    original / high; becomes f_i / factor where l_i > original / low; and between the two, with s = (original / l_i -
+    low) / (high - low), (1 - s) f_i / factor + s f_i.  cos and sin keep their magnitude."""
+    import math
+    i = torch.arange(rot // 2, dtype=torch.float64)
+    f = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / max(rot, 1))
+    if not scaling:
+        return f, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+    low, high = float(scaling["low"]), float(scaling["high"])
+    wave = 2.0 * math.pi / f
+    s = (original / wave - low) / (high - low) if high != low else torch.ones_like(f)
+    blended = (1.0 - s) * f / factor + s * f
+    out = torch.where(wave < original / high, f, torch.where(wave > original / low, f / factor, blended))
+    return out, 1.0
+
+
 @register_position_encoding("rope_live")
 class RopeLive(PositionEncoding):
     """A rotation of the first rotary_dim elements of a head without a table: the mixer's kernel takes the angle
     position * frequency in 64-bit and its cos and sin once per token.  params: rotary_dim, theta, pairing ("half":
     element i with i + rotary_dim / 2; "neighbours": element 2i with 2i + 1), scaling (None or the mapping that
-    bent_frequencies describes).  frequencies64(): float64 [rotary_dim / 2] on the device; magnitude: what cos and sin
+    bent_frequencies describes; with rule "banded" the mapping that banded_frequencies describes).  frequencies64(): float64 [rotary_dim / 2] on the device; magnitude: what cos and sin
     are multiplied by."""
 
     def load(self, tensors, rt):
@@ -109,10 +129,13 @@ class RopeLive(PositionEncoding):
         if self.pairing not in ("half", "neighbours"):
             raise ValueError(f"rope_live: pairing {self.pairing!r}")
         self.rotary_dim = rot
-        key = ("rope_live", rot, theta, tuple(sorted(scaling.items())) if scaling else None)
+        rule = self.spec.get("rule", "bent")
+        if rule not in ("bent", "banded"):
+            raise ValueError(f"rope_live: rule {rule!r}")
+        key = ("rope_live", rot, theta, rule, tuple(sorted(scaling.items())) if scaling else None)
         made = rt.shared.get(key)
         if made is None:
-            f, magnitude = bent_frequencies(rot, theta, scaling)
+            f, magnitude = (banded_frequencies if rule == "banded" else bent_frequencies)(rot, theta, scaling)
             made = rt.shared[key] = (f.to(rt.device), float(magnitude))
         self._frequencies64, self.magnitude = made
 
