@@ -80,7 +80,7 @@ def frequencies(rot):
 
 def rotate(x, positions, rot, dtype):
     """x [T, heads, dim]: the first rot.dims numbers of every head turned by position * frequency."""
-    R = int(rot["dims"])
+    R = int(rot["dims"]) if rot else 0
     if R == 0:
         return x
     f = frequencies(rot)
@@ -132,8 +132,8 @@ def mixer_attention(w, p, x, m, positions, eps, dtype):
     q, k, v = x @ w[p + "q"].T, x @ w[p + "k"].T, x @ w[p + "v"].T
     if m.get("conv"):
         q, k, v = (causal_conv(u, w[p + n + ".conv"]) for u, n in ((q, "q"), (k, "k"), (v, "v")))
-    q = rotate(q.reshape(T, H, d), positions, m["rot"], dtype)
-    k = rotate(k.reshape(T, G, d), positions, m["rot"], dtype)
+    q = rotate(q.reshape(T, H, d), positions, m.get("rot"), dtype)
+    k = rotate(k.reshape(T, G, d), positions, m.get("rot"), dtype)
     o = softmax_attention(q, k, v.reshape(T, G, dv), float(m["scale"]), sink=np.zeros(H))
     o = o.reshape(T, H * dv) * sigmoid(x @ w[p + "g"].T)
     return o @ w[p + "o"].T
@@ -147,8 +147,8 @@ def mixer_attention_2(w, p, x, m, positions, eps, dtype):
     v = x @ w[p + "v"].T + w[p + "v.b"]
     q = rms_norm(q, w[p + "q.norm"], eps)
     k = rms_norm(k, w[p + "k.norm"], eps)
-    q = rotate(q.reshape(T, H, d), positions, m["rot"], dtype)
-    k = rotate(k.reshape(T, G, d), positions, m["rot"], dtype)
+    q = rotate(q.reshape(T, H, d), positions, m.get("rot"), dtype)
+    k = rotate(k.reshape(T, G, d), positions, m.get("rot"), dtype)
     o = softmax_attention(q, k, v.reshape(T, G, dv), float(m["scale"]), softcap=float(m.get("softcap") or 0.0),
                           sink=w[p + "sink"])
     return o.reshape(T, H * dv) @ w[p + "o"].T
@@ -157,8 +157,8 @@ def mixer_attention_2(w, p, x, m, positions, eps, dtype):
 def mixer_retention(w, p, x, m, positions, eps, dtype):
     H, d, dv = m["heads"], m["dim"], m["vdim"]
     T = x.shape[0]
-    q = rotate((x @ w[p + "q"].T).reshape(T, H, d), positions, m["rot"], dtype)
-    k = rotate((x @ w[p + "k"].T).reshape(T, H, d), positions, m["rot"], dtype) * dtype(d ** -0.5)
+    q = rotate((x @ w[p + "q"].T).reshape(T, H, d), positions, m.get("rot"), dtype)
+    k = rotate((x @ w[p + "k"].T).reshape(T, H, d), positions, m.get("rot"), dtype) * dtype(d ** -0.5)
     v = (x @ w[p + "v"].T).reshape(T, H, dv)
     o = np.zeros((T, H, dv), dtype=dtype)
     for h in range(H):
