@@ -208,7 +208,9 @@ def test_attention_finds_a_key_far_away_and_at_page_borders(kind, cap, dtype):
     for j, i in marked.items():
         key = plain.rotate((x[j:j + 1] @ w["k"].T).reshape(1, G, d), [j], r, np.float64)       # as the cache holds it
         back = plain.rotate(np.repeat(key, H, axis=1), [-i], r, np.float64).reshape(-1)        # q_i turned to i is the key
-        x[i] = np.linalg.lstsq(w["q"], back * 30.0 / np.abs(back).max(), rcond=None)[0]
+        # x[i] is chosen so that Wq x[i] is that query, enlarged, and Wk x[i] = 0 (its own key does not draw it)
+        x[i] = np.linalg.lstsq(np.concatenate([w["q"], w["k"]]),
+                               np.concatenate([back * 30.0 / np.abs(back).max(), np.zeros(G * d)]), rcond=None)[0]
     if dtype == "bfloat16":
         x = tu.bf16(x).astype(np.float64)
     m = dict(heads=H, kv_heads=G, dim=d, vdim=dv, scale=scale, softcap=cap, rot=r)
@@ -258,7 +260,7 @@ def test_retention_carries_its_state_through_portions_and_slots(H, d, dv, r, dty
                                                              "rule": "banded", "scaling": r.get("scaling")})
     part = load(Retention(PartSpec("retention", {"hidden": E, "heads": H, "head_dim": d, "v_dim": dv, "decay": decay,
                                                  "eps": eps, "position": position}), "m."), w, dtype)
-    cache = CacheManager([part.cache_needs()], 16, 8, 3, dtype=DT[dtype], device=DEV)
+    cache = CacheManager([part.cache_needs()], 16, 40, 3, dtype=DT[dtype], device=DEV)
     cache.open("other")
     steps = [[("a", 3)], [("a", 61), ("b", 1)], [("b", 2), ("a", 1)], [("a", 150), ("b", 40)], [("a", 2)], [("a", 1), ("b", 1)],
              [("b", 31), ("a", 1)], [("a", 30)], [("a", 70)], [("a", 1)]]
