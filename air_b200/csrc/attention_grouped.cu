@@ -11,7 +11,8 @@
 //   its heads' numbers 16 bytes at a time.  Softmax: online, one warp per head in turn, 32-bit.  Weighted values: a
 //   thread takes the words tid, tid + 256, .. of the value rows for all JB heads, whose weights it fetches 16 bytes at
 //   a time.  The block writes unnormalised sums, its maximum and its sum of
-//   weights; grouped_combine_kernel merges the splits in order, adds the sink's term to the denominator and rounds
+//   weights; grouped_combine_kernel merges the splits in order, adds the sink's term to the denominator (and multiplies by
+//   the sigmoid of a gate logit per output element, where the layer has such gates) and rounds
 //   once.  What a query computes depends on its position, the split count and the cache only.
 //
 // q: [T, H, d] (float32, or the cache's type); cache: pages of keys [G, P, d] then values [G, P, dv], or (latent)
@@ -448,7 +449,7 @@ grouped_attention_tc_kernel(const void* __restrict__ q_any, int q_f32, const __n
 template <typename T>
 __global__ void __launch_bounds__(128)
 grouped_combine_kernel(const float* __restrict__ part, const int* __restrict__ token_seq, const float* __restrict__ sink,
-                       T* __restrict__ out, int H, int dv, int splits) {
+                       T* __restrict__ out, int H, int dv, int splits, const float* __restrict__ gate, int ldg) {
     pdl_enter(TR_ATT_GROUPED);
     const int t = blockIdx.x, h = blockIdx.y;
     if (token_seq[t] < 0) return;
@@ -467,7 +468,9 @@ grouped_combine_kernel(const float* __restrict__ part, const int* __restrict__ t
             const float ms = p[s * (dv + 2) + dv];
             if (ms != -INFINITY) o += p[s * (dv + 2) + c] * expf(ms - m);
         }
-        out[((size_t)t * H + h) * dv + c] = from_float<T>(o * inv);
+        // (a gate per output element: the logits' sigmoid multiplies as the row is written)
+        const float g = gate ? 1.f / (1.f + expf(-gate[(size_t)t * ldg + h * dv + c])) : 1.f;
+        out[((size_t)t * H + h) * dv + c] = from_float<T>(o * inv * g);
     }
 }
 
@@ -494,7 +497,8 @@ int launch_grouped(const void* q, int q_f32, const void* cache, const int* block
 AIR_API int air_grouped_attention(const void* q, int q_f32, const void* cache, int dtype, const int* block_table,
                                   int max_blocks, const int* token_seq, const int* positions, float* part, void* out,
                                   int T, int H, int G, int d, int dv, int P, int window, float scale, int mask_mode,
-                                  const float* sink, int latent, int splits, float softcap, cudaStream_t stream) {
+                                  const float* sink, int latent, int splits, float softcap, const float* gate, int ldg,
+                                  cudaStream_t stream) {
     if (T <= 0) return 0;
     const int bytes = dtype == AIR_F32 ? 4 : 2;
     if (d <= 0 || dv <= 0 || dv > (dtype == AIR_F32 ? 768 : 1024) || (d * bytes) % 16 || (dv * bytes) % 16 || H <= 0 || G <= 0 ||
@@ -519,7 +523,7 @@ AIR_API int air_grouped_attention(const void* q, int q_f32, const void* cache, i
                              splits, stages);
             if (rc) return rc;
             return air::launch(air::grouped_combine_kernel<__nv_bfloat16>, dim3(T, H), 128, 0, stream, part, token_seq,
-                               sink, (__nv_bfloat16*)out, H, dv, splits);
+                               sink, (__nv_bfloat16*)out, H, dv, splits, gate, ldg);
         }
     }
     AIR_DISPATCH(dtype, TT, {
@@ -531,7 +535,7 @@ AIR_API int air_grouped_attention(const void* q, int q_f32, const void* cache, i
                                             G, d, dv, P, window, mask_mode, scale, softcap, latent, splits, stream);
         if (rc) return rc;
         return air::launch(air::grouped_combine_kernel<TT>, dim3(T, H), 128, 0, stream, part, token_seq, sink, (TT*)out,
-                           H, dv, splits);
+                           H, dv, splits, gate, ldg);
     });
     return 0;
 }

@@ -15,6 +15,7 @@
 //   EPI_F32 / EPI_BF16  store C
 //   EPI_SILU            W holds, per tile, BN/2 rows of the gate projection followed by the BN/2 rows
 //                       of the up projection for the same outputs: out = silu(gate) * up as bfloat16
+//   EPI_RELU2           store max(C, 0)^2 as bfloat16 (the hidden layer of a feed-forward without a gate)
 //   EPI_PARTIAL         the k range is split over `splits` blocks; each writes its partial sums to
 //                       C[split][M][N] (float32), which the consumer (norm or rotary kernel) adds up
 //                       in a fixed order.  This keeps all 148 SMs streaming weights when M is small.
@@ -39,7 +40,7 @@ constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;
 constexpr int TC_THREADS = 192;       // 320 with AR = 256: eight epilogue warps
 
-enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_SILU = 2, EPI_PARTIAL = 3 };
+enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_SILU = 2, EPI_PARTIAL = 3, EPI_RELU2 = 4 };
 
 struct TcArgs {
     void* out;          // EPI_F32/PARTIAL: float [splits][M][N]; EPI_BF16: bf16 [M][N]; EPI_SILU: bf16 [M][N/2]
@@ -256,13 +257,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         uint32_t v[32];
                         tmem_ld32(taddr + c, v);
                         if (row < args.M) {
-                            if (EPI == EPI_BF16) {
+                            if (EPI == EPI_BF16 || EPI == EPI_RELU2) {
                                 __nv_bfloat16* out = (__nv_bfloat16*)args.out + (size_t)row * args.N + n0 + c;
 #pragma unroll
                                 for (int j = 0; j < 32; j += 4) {
                                     if (n0 + c + j >= args.N) break;
-                                    const float y[4] = {__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                        __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])};
+                                    float y[4] = {__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                  __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])};
+                                    if (EPI == EPI_RELU2) {
+#pragma unroll
+                                        for (int e = 0; e < 4; ++e) {
+                                            const float r = fmaxf(y[e], 0.f);
+                                            y[e] = r * r;
+                                        }
+                                    }
                                     store4(out + j, y);
                                 }
                             } else {
@@ -330,6 +338,7 @@ static int dispatch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, c
             if constexpr (BN >= 64) return launch_tc<BN, EPI_SILU, AR>(ma, mw, args, blocks, stream);
             return AIR_ERR_BAD_ARGUMENT;
         case EPI_PARTIAL: return launch_tc<BN, EPI_PARTIAL, AR>(ma, mw, args, blocks, stream);
+        case EPI_RELU2: return launch_tc<BN, EPI_RELU2, AR>(ma, mw, args, blocks, stream);
         default: return AIR_ERR_BAD_ARGUMENT;
     }
 }

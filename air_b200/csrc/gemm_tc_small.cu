@@ -17,6 +17,7 @@
 //   EPI_F32 / EPI_BF16  store C
 //   EPI_SILU            HALVES = 2 and W holds, per 256 rows, 128 rows of the gate projection followed
 //                       by the 128 rows of the up projection for the same outputs: silu(gate) * up
+//   EPI_RELU2           store max(C, 0)^2 as bfloat16 (the hidden layer of a feed-forward without a gate)
 //   EPI_PARTIAL         the k range is split over `splits` blocks; each writes C[split][T][N] (float32)
 // Rows of X beyond T and rows of W beyond N are zero-filled by TMA.
 // Every wait on an mbarrier is bounded; on giving up the block sets *status = 4 (as gemm_tc.cu).
@@ -29,7 +30,7 @@ namespace air {
 constexpr int TS_BK = 64;
 constexpr int TS_THREADS = 192;
 
-enum { TS_F32 = 0, TS_BF16 = 1, TS_SILU = 2, TS_PARTIAL = 3 };   // as in gemm_tc.cu
+enum { TS_F32 = 0, TS_BF16 = 1, TS_SILU = 2, TS_PARTIAL = 3, TS_RELU2 = 4 };   // as in gemm_tc.cu
 
 struct TsArgs {
     void* out;          // F32/PARTIAL: float [splits][T][N]; BF16: bf16 [T][N]; SILU: bf16 [T][N/2]
@@ -270,6 +271,13 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 #pragma unroll
                             for (int t = 0; t < NT; ++t)
                                 if (t < args.T) out[(size_t)t * args.N] = __float2bfloat16_rn(v[t]);
+                        } else if constexpr (EPI == TS_RELU2) {
+                            __nv_bfloat16* out = (__nv_bfloat16*)args.out + col;
+#pragma unroll
+                            for (int t = 0; t < NT; ++t) {
+                                const float r = fmaxf(v[t], 0.f);
+                                if (t < args.T) out[(size_t)t * args.N] = __float2bfloat16_rn(r * r);
+                            }
                         } else {
                             float* out = (float*)args.out + (size_t)split * args.T * args.N + col;
 #pragma unroll
@@ -328,6 +336,7 @@ static int ts_dispatch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& mx
             if constexpr (HALVES == 2) return ts_launch<NT, TS_SILU, HALVES>(mw, mx, args, blocks, stream);
             return AIR_ERR_BAD_ARGUMENT;
         case TS_PARTIAL: return ts_launch<NT, TS_F32, HALVES>(mw, mx, args, blocks, stream);
+        case TS_RELU2: return ts_launch<NT, TS_RELU2, HALVES>(mw, mx, args, blocks, stream);
         default: return AIR_ERR_BAD_ARGUMENT;
     }
 }

@@ -45,7 +45,7 @@ _SIGNATURES = {
                            c_void_p, c_void_p],
     "air_grouped_attention": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_int,
-                              c_float, c_void_p],
+                              c_float, c_void_p, c_int, c_void_p],
     "air_gather_keys": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                         c_void_p, c_void_p],
     "air_masked_softmax": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -452,11 +452,17 @@ def grouped_attention_ok(cache_dtype, d, dv) -> bool:
 
 
 def grouped_attention(q, cache, block_table, token_seq, positions, out, window, scale, kv_heads=1, page_tokens=None,
-                      chunk=None, sink=None, latent=False, splits=None, softcap=0.0):
+                      chunk=None, sink=None, latent=False, splits=None, softcap=0.0, gate=None):
     """paged_attention_ref's arithmetic and arguments (32-bit, any batch, window or chunk, sink, latent rows), by the
     kernel in which a block serves all query heads of a key/value head and the keys of a token are split over
-    `splits` blocks (default: enough to fill the device); needs grouped_attention_ok(cache.dtype, d, dv)."""
+    `splits` blocks (default: enough to fill the device); needs grouped_attention_ok(cache.dtype, d, dv).  gate (float32
+    [T, H * dv], may be a band of columns): out is multiplied, element by element, by sigmoid(gate)."""
     T, H, d = q.shape
+    gp, ldg = (None, 0)
+    if gate is not None:
+        gp, ldg = _columns(gate, "gate")
+        if tuple(gate.shape) != (T, H * out.shape[2]):
+            raise KernelError("grouped_attention: the gate does not fit")
     dv = out.shape[2]
     _req(q, "q", _FLOATS)
     G = 1 if latent else int(kv_heads)
@@ -491,7 +497,7 @@ def grouped_attention(q, cache, block_table, token_seq, positions, out, window, 
         q.data_ptr(), 1 if q.dtype == torch.float32 else 0, cache.data_ptr(), _DT[cache.dtype], block_table.data_ptr(),
         block_table.shape[1], token_seq.data_ptr(), positions.data_ptr(), part.data_ptr(), out.data_ptr(), T, H, G, d,
         dv, P, int(chunk or window or 0), float(scale), 1 if chunk else 0, _ptr(sink), 1 if latent else 0, int(splits),
-        float(softcap or 0.0), _stream()), "grouped_attention")
+        float(softcap or 0.0), gp, ldg, _stream()), "grouped_attention")
     global launches
     launches += 1
     return out
@@ -1220,7 +1226,7 @@ def prefill_attention(q, cache, block_table, tiles, out, window, scale, status=N
     return out
 
 
-EPI_F32, EPI_BF16, EPI_SILU, EPI_PARTIAL = 0, 1, 2, 3
+EPI_F32, EPI_BF16, EPI_SILU, EPI_PARTIAL, EPI_RELU2 = 0, 1, 2, 3, 4
 
 
 SILU = (1.0, 0.0, 0.0)      # the gated activation of EPI_SILU as (alpha, limit, shift): see gemm_tc
@@ -1235,7 +1241,7 @@ def gemm_tc(a, w, out, bn, epi, splits=1, status=None, max_blocks=0, force_rows_
     epi EPI_F32: out float32 [M,N]; EPI_BF16: out bfloat16 [M,N]; EPI_SILU: w holds gate and up rows
     interleaved in blocks of bn/2, out bfloat16 [M,N/2] = silu(gate)*up, or with act = (alpha, limit, shift)
     g * sigmoid(alpha * g) * (u + shift) where g = min(gate, limit), u = clamp(up, -limit, limit) if limit > 0;
-    EPI_PARTIAL: out float32
+    EPI_RELU2: out bfloat16 [M,N] = max(product, 0)^2; EPI_PARTIAL: out float32
     [splits,M,N] partial sums over parts of k.  With up to 64 rows and bn 128 or 256 the product runs with the
     weights as the M side of the instruction (gemm_tc_small.cu) unless force_rows_as_m."""
     M, K = a.shape
@@ -1248,7 +1254,7 @@ def gemm_tc(a, w, out, bn, epi, splits=1, status=None, max_blocks=0, force_rows_
         raise KernelError(f"gemm_tc: tile width {bn}")
     if epi == EPI_F32:
         _req(out, "out", (torch.float32,), (M, N))
-    elif epi == EPI_BF16:
+    elif epi in (EPI_BF16, EPI_RELU2):      # EPI_RELU2: out = max(product, 0)^2
         _req(out, "out", (torch.bfloat16,), (M, N))
     elif epi == EPI_SILU:
         _req(out, "out", (torch.bfloat16,), (M, N // 2))

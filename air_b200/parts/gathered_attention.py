@@ -53,18 +53,26 @@ class PortionAttention:
             return position - position % self.chunk
         return 0
 
-    def attend(self, q, cache, bt, ctx, out, *, latent=False, kv_heads=1, page_tokens=None):
-        """out [T, H, dv] = attention of q [T, H, dk] (float32, or the cache's type) over the request's pages."""
+    def attend(self, q, cache, bt, ctx, out, *, latent=False, kv_heads=1, page_tokens=None, gate=None):
+        """out [T, H, dv] = attention of q [T, H, dk] (float32, or the cache's type) over the request's pages.  gate
+        (float32 [T, H * dv] logits, may be a band of columns): out is multiplied by sigmoid(gate) element by element,
+        in the kernel that merges the key splits where that kernel attends, else by a kernel of its own."""
         sinks = getattr(self, "sinks", None)
         softcap = float(getattr(self, "softcap", 0.0) or 0.0)
         plan = ctx.plans.get((self.PLAN,)) if not self.rt.is_fp32 else None
 
         def through_the_pages(token_seq):
             # (the kernel that reads a key once for all heads of its group wants rows of whole 16-byte pieces)
-            kernel = ops.grouped_attention if ops.grouped_attention_ok(cache.dtype, q.shape[2], out.shape[2]) \
-                else ops.paged_attention_ref
-            kernel(q, cache, bt, token_seq, ctx.positions, out, self.window, self.scale, kv_heads=kv_heads,
-                   page_tokens=page_tokens, chunk=self.chunk, sink=sinks, latent=latent, softcap=softcap)
+            if ops.grouped_attention_ok(cache.dtype, q.shape[2], out.shape[2]):
+                ops.grouped_attention(q, cache, bt, token_seq, ctx.positions, out, self.window, self.scale,
+                                      kv_heads=kv_heads, page_tokens=page_tokens, chunk=self.chunk, sink=sinks,
+                                      latent=latent, softcap=softcap, gate=gate)
+                return
+            ops.paged_attention_ref(q, cache, bt, token_seq, ctx.positions, out, self.window, self.scale,
+                                    kv_heads=kv_heads, page_tokens=page_tokens, chunk=self.chunk, sink=sinks,
+                                    latent=latent, softcap=softcap)
+            if gate is not None:
+                ops.sigmoid_gate(out.view(out.shape[0], -1), gate, token_seq)
 
         if plan is None or not plan.portions:
             through_the_pages(ctx.token_seq)
@@ -105,4 +113,6 @@ class PortionAttention:
                     dst.copy_(summed.view(nb, H, dv))
                 else:
                     dst.view(nb, G, J, dv).copy_(summed.view(G, nb, J, dv).permute(1, 0, 2, 3))
+            if gate is not None:
+                ops.sigmoid_gate(out[r0:r0 + n].view(n, H * dv), gate[r0:r0 + n], ctx.token_seq[r0:r0 + n])
         return out

@@ -102,6 +102,12 @@ class Linear:
         return ops.gemm_tc(x, self.weight, out, 2 * self.gate_up_block, ops.EPI_SILU, status=self.status, act=act,
                            **scale)
 
+    def relu2(self, x) -> torch.Tensor:
+        """bfloat16 [rows, out] = max(x W^T, 0)^2, in the epilogue of the tcgen05 kernel."""
+        bn, _ = choose_tile(self.out_features, self.in_features, may_split=False)
+        out = torch.empty((x.shape[0], self.out_features), dtype=torch.bfloat16, device=x.device)
+        return ops.gemm_tc(x, self.weight, out, bn, ops.EPI_RELU2, status=self.status)
+
     def f32(self, x: torch.Tensor) -> torch.Tensor:
         """float32 [rows, out], complete sums: the tcgen05 kernel in one pass for few rows of 16-bit weights, else the
         product that __call__ picks."""

@@ -172,9 +172,9 @@ class Relu2MLP(FeedForward):
     the rectifier.  params: hidden, intermediate.  Tensors: <prefix>up [intermediate, hidden], down [hidden,
     intermediate].
 
-    The hidden layer leaves the first product in 32-bit where the step has few rows (the tcgen05 product for few rows)
-    or the engine is float32, else in the compute dtype; one kernel squares the rectified values and writes them in the
-    compute dtype."""
+    In bfloat16 the tcgen05 product squares the rectified sums in its epilogue (32-bit, rounded once), for few rows and
+    for as many as that kernel is at least as fast as the library's (fused_gate_up_pays); else the library's product is
+    followed by the kernel that squares the rectified values (from 32-bit sums in a float32 engine)."""
 
     graph_safe = True
 
@@ -189,9 +189,10 @@ class Relu2MLP(FeedForward):
         self.down = Linear(tensors[self.prefix + "down"], rt.status)
 
     def forward(self, x, ctx):
-        if self.rt.is_fp32 or self.up.small(x):
-            z = self.up.f32(x)
+        if self.up.tc_ok and x.dtype == torch.bfloat16 and (self.up.small(x) or
+                                                            fused_gate_up_pays(x.shape[0], self.up.out_features)):
+            act = self.up.relu2(x)
         else:
-            z = self.up(x, self.rt.dtype)
-        act = ops.relu2(z, torch.empty(z.shape, dtype=self.rt.dtype, device=x.device))
+            z = self.up(x, torch.float32 if self.rt.is_fp32 else self.rt.dtype)
+            act = ops.relu2(z, torch.empty(z.shape, dtype=self.rt.dtype, device=x.device))
         return self.down.f32_sums(act)

@@ -158,7 +158,5 @@ class NormedAttention(PortionAttention, Mixer):
                               pos.magnitude, ctx.positions, ctx.token_seq, bt, q, kv, G, dv, P, status=ctx.status,
                               bias=self.bias, whole=self.norm_whole)
         out = torch.empty((T, H, dv), dtype=rt.dtype, device=x.device)
-        self.attend(q, kv, bt, ctx, out, kv_heads=G, page_tokens=P)
-        if self.out_gate:
-            ops.sigmoid_gate(out.view(T, H * dv), full[:, C:], ctx.token_seq)
+        self.attend(q, kv, bt, ctx, out, kv_heads=G, page_tokens=P, gate=full[:, C:] if self.out_gate else None)
         return self.o.f32_sums(out.view(T, H * dv))

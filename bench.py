@@ -517,6 +517,30 @@ def _pefivik(width, layers, heads, kv_heads, ff, vocab=32000):
             "layers": [dict(hgrn if i % 4 == 2 else latent, mlp=moe if i % 2 else dense) for i in range(n)]}
 
 
+# Tabopel beside Tomodra, the closest of the other designs (grouped-query attention with a sink through the same mixer
+# class, a mixture of experts), at equal width, heads and number of runs (`--design tabopel`): attention behind
+# convolutions of four taps, attention with whole-vector norms and a soft cap, retention, attention, in turn, heads of
+# 128; dense feed-forwards of 3 ff / 2 (as many weights as a gated one of ff) and mixtures of 16 experts of 3 ff / 8
+# beside 2 identity experts, of which a token takes 4, in turn; two of its layers run twice, so `layers` runs are
+# layers - 2 layers' weights.
+def _tabopel(width, layers, heads, kv_heads, ff, vocab=32000):
+    scaling = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}
+    first = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "conv": 4,
+                                            "scale": 128 ** -0.5, "rot": {"dims": 128, "base": 5e5, "scaling": scaling}}}
+    second = {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128,
+                                               "scale": 128 ** -0.5, "softcap": 50.0, "rot": {"dims": 64, "base": 5e5}}}
+    ret = {"type": "retention", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "rot": {"dims": 128, "base": 1e6},
+                                          "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(1, heads - 1)) for h in range(heads)]}}
+    dense = {"kind": "dense", "ff": 3 * ff // 2}
+    moe = {"kind": "moe", "expert": {"ff": 3 * ff // 8}, "router": {"experts": 16, "identity": 2, "top": 4}}
+    n = max(2, layers - 2)
+    start = min(1, n - 2)
+    order = [first, second, ret, first]
+    return {"architecture": "Tabopel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 8.0},
+            "loop": {"start": start, "stop": start + 2, "times": 2},
+            "layers": [dict(order[i % 4], mlp=moe if i % 2 else dense) for i in range(n)]}
+
+
 def _qwen(width, layers, heads, kv_heads, ff, vocab=32000):
     return dict(_QWEN, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
                 num_key_value_heads=kv_heads, intermediate_size=ff, rms_norm_eps=1e-5, max_window_layers=layers,
@@ -1003,12 +1027,192 @@ def pefivik_kernels(width, heads, kv_heads, ff, T, batch, context):
     return rows
 
 
+def tabopel_kernels(width, heads, kv_heads, ff, T, batch, context):
+    """Tabopel's kernels alone at the layer's shapes, each beside the like kernel of Tomodra, Pefivik, Bivizen or the
+    Qwen2 decoder, from memory (512 MB written before each launch, the writes' own time subtracted): microseconds, and
+    the share of the measured copy rate (bytes) or of the measured bf16 rate (flops) that the algorithm's bytes or
+    flops make."""
+    import torch
+    from air_b200.csrc import ops
+    pk = peaks()
+    big = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+
+    def graph_time(calls, reps=5):
+        for c in calls:
+            c()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(reps):
+                for c in calls:
+                    c()
+        graph.replay()
+        torch.cuda.synchronize()
+        us = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            us.append(a.elapsed_time(b) * 1e3 / reps)
+        return statistics.median(us)
+
+    flush = lambda: big.zero_()
+    t_flush = graph_time([flush])
+    rows = []
+
+    def report(name, f, nbytes=0, flops=0):
+        us = graph_time([flush, f]) - t_flush
+        frac = (nbytes / us / 1e3 / pk["hbm_gbs"]) if nbytes else (flops / us / 1e6 / pk["bf16_tflops"])
+        rows.append({"kernel": name, "us": round(us, 1), "of": "copy rate" if nbytes else "bf16 rate", "frac": round(frac, 3)})
+        print(f"  {name:70s} {us:8.1f} us  {frac:5.2f} of the measured {'copy' if nbytes else 'bf16'} rate", flush=True)
+
+    E, H, G, d, P = width, heads, kv_heads, 128, 64
+    n_exp, ident, top, F = 16, 2, 4, 3 * ff // 8
+    dev, bf, f32 = "cuda", torch.bfloat16, torch.float32
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    for label, N, entries in (("prompt", T, [(0, T)]), ("decode", batch, [(context, 1)] * batch)):
+        print(f"{label}: {N} rows, width {E}, {H}/{G} heads of {d}, {n_exp} + {ident} experts of {F}, top {top}")
+        S = len(entries)
+        starts = [0]
+        for _, n in entries:
+            starts.append(starts[-1] + n)
+        q_start, slots = i32(starts), i32(list(range(S)))
+        positions = torch.cat([torch.arange(p, p + n, dtype=torch.int32) for p, n in entries]).to(dev)
+        seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, (_, n) in enumerate(entries)]).to(dev)
+        per_request = -(-(max(p + n for p, n in entries)) // P)
+        bt = torch.arange(S * per_request, dtype=torch.int32, device=dev).view(S, per_request).contiguous()
+        longest = max(n for _, n in entries)
+        # ---- the norm behind a sub-layer, the sum and the norm ahead of the next one, beside the sums with one norm
+        h, a = torch.randn(N, E, device=dev), torch.randn(N, E, device=dev)
+        parts4 = torch.randn(top, N, E, device=dev)
+        wb, w = torch.rand(E, device=dev) + 0.5, torch.rand(E, device=dev) + 0.5
+        wbf = w.to(bf)
+        x = torch.empty(N, E, dtype=bf, device=dev)
+        report("normed_add_norm (norm of the term, stream + term, norm)", lambda: ops.normed_add_norm(h, a, wb, 1e-6, w, 1e-6, x), N * E * 14)
+        report("  Qwen2: add_rmsnorm (stream + term, norm)", lambda: ops.add_rmsnorm(h, a, wbf, 1e-6, x), N * E * 14)
+        report("normed_add_norm with the experts' four planes", lambda: ops.normed_add_norm(h, parts4, wb, 1e-6, w, 1e-6, x), N * E * (10 + 4 * top))
+        report("  Pefivik: scaled_norm with two planes and the shared expert",
+               lambda: ops.scaled_norm(h, [(parts4[:2], wb), (a, wb)], wbf, 1e-6, x), N * E * (10 + 12))
+        # ---- the convolutions behind the projections, beside the delta rule's (with SiLU)
+        C = (H + G) * d + G * d
+        proj = torch.randn(N, C + H * d, device=dev)
+        cw, tail = torch.randn(C, 4, device=dev), torch.zeros(S, C, 3, device=dev)
+        y = torch.empty(N, C, device=dev)
+        report("short_conv, 4 taps, no activation (q, k, v)", lambda: ops.short_conv_silu(proj[:, :C], cw, tail, y, q_start, slots, longest, act=False), N * C * 8)
+        report("  Bivizen: short_conv_silu", lambda: ops.short_conv_silu(proj[:, :C], cw, tail, y, q_start, slots, longest), N * C * 8)
+        # ---- bias, whole-vector norm, rotation, page write, beside the norm per head
+        pages = torch.zeros(S * per_request, G * P * 2 * d, dtype=bf, device=dev)
+        qo = torch.empty(N, H, d, dtype=bf, device=dev)
+        freq = torch.rand(d // 2, dtype=torch.float64, device=dev)
+        bias = torch.randn(C, device=dev)
+        qw, kw = torch.rand(H * d, device=dev), torch.rand(G * d, device=dev)
+        nbytes = N * C * 4 + N * C * 2
+        report("qk_normed_prepare (bias, norm of the whole of q and of k, rotation)",
+               lambda: ops.qk_normed_prepare(y, qw, kw, 1e-6, freq[:d // 4], "half", 1.0, positions, seq, bt, qo, pages, G, d, P, bias=bias, whole=True), nbytes)
+        report("qk_normed_prepare (no norm, rotation of the whole head)",
+               lambda: ops.qk_normed_prepare(y, None, None, 1e-6, freq, "half", 1.0, positions, seq, bt, qo, pages, G, d, P), nbytes)
+        report("  Tomodra: qk_normed_prepare (norm per head, neighbouring pairs)",
+               lambda: ops.qk_normed_prepare(y, qw[:d].contiguous(), kw[:d].contiguous(), 1e-6, freq[:d // 4], "neighbours", 1.0, positions, seq, bt, qo, pages, G, d, P), nbytes)
+        # ---- the gate on the heads' outputs, beside the gate per head
+        out = torch.randn(N, H, d, device=dev).to(bf)
+        gate_h = torch.rand(N, H, device=dev)
+        report("sigmoid_gate (a logit per output element)", lambda: ops.sigmoid_gate(out.view(N, H * d), proj[:, C:], seq), N * H * d * 8)
+        report("  Bivizen: head_gate (a gate per head)", lambda: ops.head_gate(out, gate_h, seq), N * H * d * 4)
+        if label == "decode":
+            # ---- single tokens over the pages: cap and sink, and the gate in the merge, beside Tomodra's chunk and sink
+            sink = torch.randn(H, device=dev)
+            ao = torch.empty(N, H, d, dtype=bf, device=dev)
+            kvb = 2 * S * context * G * d * 2
+            report("grouped_attention (all keys, soft cap, learned sink)",
+                   lambda: ops.grouped_attention(qo, pages, bt, seq, positions, ao, None, d ** -0.5, kv_heads=G, page_tokens=P, sink=sink, softcap=50.0), kvb)
+            report("grouped_attention (all keys, zero sink, gates in the merge)",
+                   lambda: ops.grouped_attention(qo, pages, bt, seq, positions, ao, None, d ** -0.5, kv_heads=G, page_tokens=P, sink=torch.zeros_like(sink), gate=proj[:, C:]), kvb)
+            report("  Tomodra: grouped_attention (chunk of 1,024, sink)",
+                   lambda: ops.grouped_attention(qo, pages, bt, seq, positions, ao, None, d ** -0.5, kv_heads=G, page_tokens=P, chunk=1024, sink=sink), kvb // 2)
+        # ---- retention beside gated linear attention (the same scan with a decay per channel)
+        rq = torch.randn(N, 3 * H * d, device=dev)
+        state = torch.zeros(S, H, d, d, device=dev)
+        o = torch.empty(N, H, d, device=dev)
+        decays, dec = torch.full((H,), 0.99, device=dev), torch.randn(N, H * d, device=dev)
+        sb = (2 * S * H * d * d * 4 + N * 4 * H * d * 4) if label == "decode" else N * 4 * H * d * 4
+        report("linear_scan as retention (rotation, a constant decay per head)",
+               lambda: ops.linear_scan(ops.SCAN_RETENTION, rq[:, :H * d], rq[:, H * d:2 * H * d], rq[:, 2 * H * d:], decays, state, o, q_start, slots, seq, positions=positions, freq=freq, k_scale=d ** -0.5), sb)
+        report("  Bivizen: linear_scan as gated linear attention",
+               lambda: ops.linear_scan(ops.SCAN_GLA, rq[:, :H * d], rq[:, H * d:2 * H * d], rq[:, 2 * H * d:], dec, state, o, q_start, slots, seq, q_scale=d ** -0.5, tau=16.0), sb + N * H * d * 4)
+        ones = torch.ones(d, device=dev)
+        yo = torch.empty(N, H * d, dtype=bf, device=dev)
+        report("gated_rmsnorm (norm per head without a weight's effect, silu gate)", lambda: ops.gated_rmsnorm(o, proj[:, :H * d], ones, 1e-6, yo, seq), N * H * d * 10)
+        # ---- the squared rectifier, beside SiLU(gate) x up
+        Fd = 3 * ff // 2
+        z = torch.randn(N, Fd, device=dev).to(bf)
+        zz = torch.randn(N, 2 * ff, device=dev).to(bf)
+        act, act2 = torch.empty(N, Fd, dtype=bf, device=dev), torch.empty(N, ff, dtype=bf, device=dev)
+        report("relu2 (behind the library's product)", lambda: ops.relu2(z, act), N * Fd * 4)
+        report("  Qwen2: silu_mul", lambda: ops.silu_mul(zz, act2, block=128), N * ff * 6)
+        xin = torch.randn(N, E, device=dev).to(bf)
+        wup = torch.randn(Fd, E, device=dev).to(bf) * 0.02
+        wgu = torch.randn(2 * ff, E, device=dev).to(bf) * 0.02
+        if N <= 64 or N >= 512:
+            bn = 256 if N <= 64 else 128
+            report("gemm_tc with the squared rectifier in its epilogue (up)",
+                   lambda: ops.gemm_tc(xin, wup, act, 256 if N <= 64 else 128, ops.EPI_RELU2), flops=2 * N * Fd * E) if N > 64 else \
+                report("gemm_tc with the squared rectifier in its epilogue (up)",
+                       lambda: ops.gemm_tc(xin, wup, act, 256, ops.EPI_RELU2), nbytes=Fd * E * 2)
+            if N > 64:
+                report("  Qwen2: gemm_tc with SiLU(gate) x up in its epilogue", lambda: ops.gemm_tc(xin, wgu, act2, 256, ops.EPI_SILU), flops=4 * N * ff * E)
+            else:
+                report("  Qwen2: gemm_tc with SiLU(gate) x up in its epilogue", lambda: ops.gemm_tc(xin, wgu, act2, 256, ops.EPI_SILU), nbytes=2 * ff * E * 2)
+        # ---- the router with corrections and identity experts, the experts' two products
+        total = n_exp + ident
+        zr = torch.randn(N, 24, device=dev)
+        corr = torch.randn(total, device=dev) * 0.1
+        expert = torch.empty(N, top, dtype=torch.int32, device=dev)
+        weight = torch.empty(N, top, device=dev)
+        report("moe_route (softmax, score + correction, 18 outputs, top 4)", lambda: ops.moe_route(zr, total, top, expert, weight, score="softmax", choice_bias=corr), N * 24 * 4)
+        e2, w2 = torch.empty(N, 2, dtype=torch.int32, device=dev), torch.empty(N, 2, device=dev)
+        report("  Tomodra: moe_route (sigmoid, 16 experts, top 2)", lambda: ops.moe_route(zr, 16, 2, e2, w2, score="sigmoid"), N * 24 * 4)
+        ops.moe_route(zr, total, top, expert, weight, score="softmax", choice_bias=corr)
+        yp = torch.zeros(top, N, E, device=dev)
+        report("moe_identity (the pairs of the two identity experts)", lambda: ops.moe_identity(xin, expert, weight, n_exp, yp), N * top * 2 // total * E * 6)
+        pairs = N * top
+        ints = torch.empty(n_exp + 1 + pairs + 2 * (pairs // ops.GROUP_TILE + n_exp) + 1, dtype=torch.int32, device=dev)
+        start, pair_of_slot = ints[:n_exp + 1], ints[n_exp + 1:n_exp + 1 + pairs]
+        tiles, num_tiles = ints[n_exp + 1 + pairs:-1].view(-1, 2), ints[-1:]
+        ops.moe_sort(expert, n_exp, start, pair_of_slot, tiles, num_tiles)
+        torch.cuda.synchronize()
+        real = int(start[-1].item())
+        touched = len(set(expert.view(-1).tolist()) - set(range(n_exp, total)))
+        up = torch.randn(n_exp, F, E, device=dev).to(bf) * 0.02
+        down = torch.randn(n_exp, E, F, device=dev).to(bf) * 0.02
+        acts = torch.empty(pairs, F, dtype=bf, device=dev)
+        if label == "decode":
+            report("grouped_gemm up with the squared rectifier (few rows per expert)",
+                   lambda: ops.grouped_gemm(xin, up, acts, F, E, lda=E, ldo=F, groups=n_exp, a_index=pair_of_slot, a_div=top, start=start, tiles=tiles, num_tiles=num_tiles, relu2=True),
+                   nbytes=touched * F * E * 2)
+            report("grouped_gemm down with the weight on the output",
+                   lambda: ops.grouped_gemm(acts, down, yp, E, F, lda=F, ldo=E, groups=n_exp, o_index=pair_of_slot, o_div=top, o_part_stride=N * E, start=start, tiles=tiles, num_tiles=num_tiles, o_scale=weight.view(-1)),
+                   nbytes=touched * F * E * 2)
+        else:
+            ends = start[1:].clone()
+            rws = ops.rows_by_index(xin, pair_of_slot, top, None, torch.empty(pairs, E, dtype=bf, device=dev))
+            report("library grouped product up + relu2 (many rows per expert)",
+                   lambda: ops.relu2(torch._grouped_mm(rws, up.transpose(1, 2), offs=ends), acts), flops=2 * real * F * E)
+            report("library grouped product down + planes_by_index with the weight",
+                   lambda: ops.planes_by_index(torch._grouped_mm(acts, down.transpose(1, 2), offs=ends), pair_of_slot, top, yp, scale=weight.view(-1)),
+                   flops=2 * real * F * E)
+    return rows
+
+
 def design_bench(args):
     import torch
     from air_b200.engine.batch import Entry, LAST_SAMPLED
-    designs = {"bivizen": ("Bivizen", _bivizen), "tomodra": ("Tomodra", _tomodra), "pefivik": ("Pefivik", _pefivik)}
+    designs = {"bivizen": ("Bivizen", _bivizen), "tomodra": ("Tomodra", _tomodra), "pefivik": ("Pefivik", _pefivik),
+               "tabopel": ("Tabopel", _tabopel)}
     # the model that stands beside the design: the Qwen2 decoder, or the closest of the other designs
-    beside = {"pefivik": ("tomodra", "Tomodra", _tomodra)}.get(args.design, ("qwen2", "Qwen2ForCausalLM", _qwen))
+    beside = {"pefivik": ("tomodra", "Tomodra", _tomodra), "tabopel": ("tomodra", "Tomodra", _tomodra)} \
+        .get(args.design, ("qwen2", "Qwen2ForCausalLM", _qwen))
     if args.design not in designs:
         print(json.dumps({"error": f"--design {args.design}: the designs that are compared are {', '.join(designs)}"}))
         return 2
@@ -1027,6 +1231,8 @@ def design_bench(args):
             size["kernels"] = design_kernels(width, heads, kv_heads, ff, args.prefill_tokens, args.batch, context)
         if not args.skip_kernels and args.design == "pefivik":
             size["kernels"] = pefivik_kernels(width, heads, kv_heads, ff, args.prefill_tokens, args.batch, context)
+        if not args.skip_kernels and args.design == "tabopel":
+            size["kernels"] = tabopel_kernels(width, heads, kv_heads, ff, args.prefill_tokens, args.batch, context)
         if not args.skip_kernels and args.design == "tomodra":
             size["kernels"] = tomodra_kernels(width, heads, kv_heads, ff, args.prefill_tokens, args.batch, context)
         record["sizes"][name] = size
@@ -1108,7 +1314,7 @@ def main():
     ap.add_argument("--skip-decode", action="store_true", help="for profiling the prefill step alone")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for ncu)")
     ap.add_argument("--kernel", default="", help="prefill_attention, or prompt_elementwise (at --prefill-tokens rows): time those kernels alone and exit")
-    ap.add_argument("--design", default="", help="bivizen, tomodra or pefivik: prefill and decode of that design beside the Qwen2 decoder (pefivik: beside Tomodra) at "
+    ap.add_argument("--design", default="", help="bivizen, tomodra, pefivik or tabopel: prefill and decode of that design beside the Qwen2 decoder (pefivik and tabopel: beside Tomodra) at "
                     "equal sizes, and its kernels alone beside the like kernels (another line of output; the default "
                     "workload is not run)")
     ap.add_argument("--design-sizes", default="", help="with --design: which of the sizes 2048,4096 (default: both)")

@@ -289,6 +289,19 @@ def test_dense_feed_forward_with_the_squared_rectifier(E, F, T, dtype):
     assert np.abs(got - want).max() < (1e-4 if dtype == "float32" else 4e-2) * max(1.0, np.abs(want).max())
 
 
+@pytest.mark.parametrize("M,N,K,bn", [(600, 384, 256, 128), (1100, 512, 320, 256), (130, 96, 64, 32), (9, 512, 256, 256),
+                                      (64, 384, 128, 128)])
+def test_squared_rectifier_in_the_epilogue_of_the_tensor_core_products(M, N, K, bn):
+    """Both tcgen05 products (rows as the M side for many rows, weights as the M side for few) write max(x W^T, 0)^2."""
+    from air_b200.csrc import ops
+    rng = np.random.default_rng(M + N)
+    x, w = tu.bf16(rng.normal(size=(M, K))), tu.bf16(rng.normal(size=(N, K)) / K ** 0.5)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(dev(x, torch.bfloat16), dev(w, torch.bfloat16), out, bn, ops.EPI_RELU2)
+    want = plain.relu_squared(x.astype(np.float64) @ w.astype(np.float64).T)
+    assert np.abs(out.float().cpu().numpy() - want).max() < 1e-2 * max(1.0, np.abs(want).max())
+
+
 @pytest.mark.parametrize("n,identity,top", [(5, 1, 2), (3, 0, 3), (1, 1, 1), (4, 2, 4), (12, 0, 5), (1, 2, 2), (37, 3, 8)])
 def test_router_chooses_by_score_plus_correction_and_weighs_by_score(n, identity, top):
     """The routing kernel alone against the plain router: corrections as large as the scores, so the choice by score
