@@ -259,7 +259,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 template <int D, int CHUNK>
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       const int* __restrict__ token_seq, __nv_bfloat16* __restrict__ out, int H,
-                                      int splits) {
+                                      int splits, const float* __restrict__ sink, const float* __restrict__ gate,
+                                      int ldg) {
     pdl_enter(TR_ATT_COMBINE);
     const int t = blockIdx.y, h = blockIdx.x;
     const size_t base = ((size_t)t * H + h) * splits;
@@ -293,23 +294,33 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
             }
             mm = top;
         }
-        if (slot >= 0) out[((size_t)t * H + h) * D + col] = __float2bfloat16_rn(acc / ll);
+        if (sink) {      // one more term exp(sink[h]) in the denominator (the running maximum is in units of log2 e)
+            const float s2 = sink[h] * 1.4426950408889634f;
+            const float top = fmaxf(mm, s2);
+            const float keep = exp2f(mm - top);
+            ll = ll * keep + exp2f(s2 - top);
+            acc *= keep;
+        }
+        // (a gate per output element: the logit's sigmoid multiplies as the row is written)
+        const float g = gate && slot >= 0 ? 1.f / (1.f + expf(-gate[(size_t)t * ldg + h * D + col])) : 1.f;
+        if (slot >= 0) out[((size_t)t * H + h) * D + col] = __float2bfloat16_rn(acc / ll * g);
     }
 }
 
 // The merge kernel with all of a thread's loads in one round where the splits are up to 32.
 template <int D>
 int launch_combine(const float* part_o, const float* part_ml, const int* token_seq, __nv_bfloat16* out, int T, int H,
-                   int splits, cudaStream_t stream) {
+                   int splits, cudaStream_t stream, const float* sink = nullptr, const float* gate = nullptr,
+                   int ldg = 0) {
     const int threads = D >= 128 ? 128 : 64;
     if (splits <= 8)
         return launch(decode_combine_kernel<D, 8>, dim3(H, T), threads, 0, stream, part_o, part_ml, token_seq, out, H,
-                      splits);
+                      splits, sink, gate, ldg);
     if (splits <= 16)
         return launch(decode_combine_kernel<D, 16>, dim3(H, T), threads, 0, stream, part_o, part_ml, token_seq, out, H,
-                      splits);
+                      splits, sink, gate, ldg);
     return launch(decode_combine_kernel<D, 32>, dim3(H, T), threads, 0, stream, part_o, part_ml, token_seq, out, H,
-                  splits);
+                  splits, sink, gate, ldg);
 }
 
 template <int D>
@@ -368,6 +379,20 @@ AIR_API int air_decode_combine(const float* part_o, const float* part_ml, const 
         case 64: return launch_combine<64>(part_o, part_ml, token_seq, (__nv_bfloat16*)out, T, H, splits, stream);
         case 128: return launch_combine<128>(part_o, part_ml, token_seq, (__nv_bfloat16*)out, T, H, splits, stream);
         case 256: return launch_combine<256>(part_o, part_ml, token_seq, (__nv_bfloat16*)out, T, H, splits, stream);
+        default: return AIR_ERR_BAD_ARGUMENT;
+    }
+}
+
+// The merge with one more term exp(sink[h]) in every head's denominator (sink float32 [H] or null) and with
+// sigmoid(gate[t][h * D + col]) on every output element (gate float32 with rows of ldg floats, or null).
+AIR_API int air_decode_combine_sink(const float* part_o, const float* part_ml, const int* token_seq, void* out, int T,
+                                    int H, int D, int splits, const float* sink, const float* gate, int ldg,
+                                    cudaStream_t stream) {
+    using namespace air;
+    switch (D) {
+        case 64: return launch_combine<64>(part_o, part_ml, token_seq, (__nv_bfloat16*)out, T, H, splits, stream, sink, gate, ldg);
+        case 128: return launch_combine<128>(part_o, part_ml, token_seq, (__nv_bfloat16*)out, T, H, splits, stream, sink, gate, ldg);
+        case 256: return launch_combine<256>(part_o, part_ml, token_seq, (__nv_bfloat16*)out, T, H, splits, stream, sink, gate, ldg);
         default: return AIR_ERR_BAD_ARGUMENT;
     }
 }

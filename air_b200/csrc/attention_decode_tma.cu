@@ -420,6 +420,9 @@ int launch_decode_tma(const CUtensorMap& map, const FreshQkv& fresh, const void*
 }  // namespace air
 
 // The merge of the splits (attention_decode.cu).
+extern "C" int air_decode_combine_sink(const float* part_o, const float* part_ml, const int* token_seq, void* out, int T,
+                                       int H, int D, int splits, const float* sink, const float* gate, int ldg,
+                                       cudaStream_t stream);
 extern "C" int air_decode_combine(const float* part_o, const float* part_ml, const int* token_seq, void* out, int T,
                                   int H, int D, int splits, cudaStream_t stream);
 
@@ -428,11 +431,14 @@ namespace air {
 static int decode_attention_tma(const FreshQkv& fresh, const void* q, const void* cache, long long pages,
                                 const int* block_table, int max_blocks, const int* token_seq, const int* positions,
                                 void* out, float* part_o, float* part_ml, int T, int H, int K, int D, int P, int window,
-                                float scale, float softcap, int splits, int* status, cudaStream_t stream) {
+                                float scale, float softcap, int splits, int* status, cudaStream_t stream,
+                                const float* sink = nullptr, const float* gate = nullptr, int ldg = 0) {
     if (T <= 0) return 0;
     if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 ? 64 % P : P % 64) || splits < 1 || T > 65535 ||
         (splits > 1 && (!part_o || !part_ml)) || ((uintptr_t)cache & 15))
         return AIR_ERR_BAD_ARGUMENT;
+    // a sink or gates enter where the splits are merged: the keys are then split in two parts at least
+    if ((sink || gate) && splits < 2) return AIR_ERR_BAD_ARGUMENT;
     CUtensorMap map;
     const int map_rc = tensor_map_2d(&map, cache, pages * 2 * K * P, D, P < DT_TILE ? P : DT_TILE);
     if (map_rc) return map_rc;
@@ -453,7 +459,9 @@ static int decode_attention_tma(const FreshQkv& fresh, const void* q, const void
         default:
             return AIR_ERR_BAD_ARGUMENT;
     }
-    if (rc == 0 && splits > 1) rc = air_decode_combine(part_o, part_ml, token_seq, out, T, H, D, splits, stream);
+    if (rc == 0 && splits > 1)
+        rc = (sink || gate) ? air_decode_combine_sink(part_o, part_ml, token_seq, out, T, H, D, splits, sink, gate, ldg, stream)
+                            : air_decode_combine(part_o, part_ml, token_seq, out, T, H, D, splits, stream);
     return rc;
 }
 
@@ -468,6 +476,19 @@ AIR_API int air_decode_attention_tma(const void* q, const void* cache, long long
     return air::decode_attention_tma(air::FreshQkv{nullptr, 0, 0, nullptr, nullptr, nullptr}, q, cache, pages,
                                      block_table, max_blocks, token_seq, positions, out, part_o, part_ml, T, H, K, D, P,
                                      window, scale, softcap, splits, status, stream);
+}
+
+// The same with one more term exp(sink[h]) in every head's softmax denominator (sink float32 [H] or null) and the
+// output multiplied, element by element, by sigmoid(gate[t][h * D + col]) (gate float32, rows of ldg floats, or null);
+// both enter where the key splits are merged, so splits >= 2.
+AIR_API int air_decode_attention_tma_sink(const void* q, const void* cache, long long pages, const int* block_table,
+                                          int max_blocks, const int* token_seq, const int* positions, void* out,
+                                          float* part_o, float* part_ml, int T, int H, int K, int D, int P, int window,
+                                          float scale, float softcap, int splits, int* status, const float* sink,
+                                          const float* gate, int ldg, cudaStream_t stream) {
+    return air::decode_attention_tma(air::FreshQkv{nullptr, 0, 0, nullptr, nullptr, nullptr}, q, cache, pages,
+                                     block_table, max_blocks, token_seq, positions, out, part_o, part_ml, T, H, K, D, P,
+                                     window, scale, softcap, splits, status, stream, sink, gate, ldg);
 }
 
 // The same from the q/k/v product's output instead of q: qkv float32 [parts][T][(H + 2 K) D] (partial sums that

@@ -91,6 +91,9 @@ _SIGNATURES = {
     "air_decode_attention_tma": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p,
                                  c_void_p],
+    "air_decode_attention_tma_sink": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                      c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "air_head_gate": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "air_decode_attention_tma_fresh": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int,
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -1106,9 +1109,11 @@ def decode_splits(tokens: int, heads: int, kv_heads: int) -> int:
 
 
 def decode_attention(q, cache, block_table, token_seq, positions, out, window, scale, splits=None, scratch=None,
-                     status=None, engine="tma", softcap=0.0):
+                     status=None, engine="tma", softcap=0.0, sink=None, gate=None):
     """bfloat16 attention for one query token per request.  softcap > 0: score = softcap * tanh(scale * q.k /
-    softcap) (the copy-engine kernel only).  scratch: (float32 [T*H*splits*D], float32
+    softcap) (the copy-engine kernel only).  sink (float32 [H]): one more term exp(sink[h]) in the softmax's
+    denominator; gate (float32 [T, H * d] logits, may be a band of columns): out is multiplied by sigmoid(gate) element
+    by element; both enter where the key splits are merged (the copy-engine kernel only, two splits at least).  scratch: (float32 [T*H*splits*D], float32
     [T*H*splits*2]) or None to allocate.  engine "tma": keys and values by the copy engine into shared
     memory (attention_decode_tma.cu); "ldg": by the warps' own loads (attention_decode.cu)."""
     T, H, d = q.shape
@@ -1123,6 +1128,11 @@ def decode_attention(q, cache, block_table, token_seq, positions, out, window, s
         raise KernelError(f"decode_attention takes head sizes {DECODE_HEAD_DIMS}, not {d}")
     if splits is None:
         splits = decode_splits(T, H, K)
+    extra = sink is not None or gate is not None
+    if extra:
+        splits = max(2, splits)
+        if not (engine == "tma" and tile_pages(P)):
+            raise KernelError("decode_attention: a sink or gates are taken by the copy-engine kernel only")
     po = pm = None
     if splits > 1:
         if scratch is None:
@@ -1134,7 +1144,20 @@ def decode_attention(q, cache, block_table, token_seq, positions, out, window, s
         if po.numel() < T * H * splits * d or pm.numel() < T * H * splits * 2:
             raise KernelError("decode_attention: scratch is too small")
     global launches
-    if engine == "tma" and tile_pages(P):
+    if extra:
+        gp, ldg = (None, 0)
+        if sink is not None:
+            _req(sink, "sink", (torch.float32,), (H,))
+        if gate is not None:
+            gp, ldg = _columns(gate, "gate")
+            if tuple(gate.shape) != (T, H * d):
+                raise KernelError("decode_attention: the gate does not fit")
+        _check(_get("air_decode_attention_tma_sink")(
+            q.data_ptr(), cache.data_ptr(), cache.shape[0], block_table.data_ptr(), block_table.shape[1],
+            token_seq.data_ptr(), positions.data_ptr(), out.data_ptr(), _ptr(po), _ptr(pm), T, H, K, d, P,
+            int(window or 0), float(scale), float(softcap or 0.0), splits, _ptr(status), _ptr(sink), gp, ldg,
+            _stream()), "decode_attention_tma")
+    elif engine == "tma" and tile_pages(P):
         _check(_get("air_decode_attention_tma")(
             q.data_ptr(), cache.data_ptr(), cache.shape[0], block_table.data_ptr(), block_table.shape[1],
             token_seq.data_ptr(), positions.data_ptr(), out.data_ptr(), _ptr(po), _ptr(pm), T, H, K, d, P,

@@ -53,15 +53,24 @@ class PortionAttention:
             return position - position % self.chunk
         return 0
 
-    def attend(self, q, cache, bt, ctx, out, *, latent=False, kv_heads=1, page_tokens=None, gate=None):
+    def attend(self, q, cache, bt, ctx, out, *, latent=False, kv_heads=1, page_tokens=None, gate=None, pages=None):
         """out [T, H, dv] = attention of q [T, H, dk] (float32, or the cache's type) over the request's pages.  gate
         (float32 [T, H * dv] logits, may be a band of columns): out is multiplied by sigmoid(gate) element by element,
-        in the kernel that merges the key splits where that kernel attends, else by a kernel of its own."""
+        in the kernel that merges the key splits where that kernel attends, else by a kernel of its own.  pages: the
+        cache as [pages, 2, K, P, d] where keys and values have one size: single tokens and short portions of a bfloat16
+        engine then take the copy-engine kernel of the dense decoder (heads of 64, 128 or 256, pages that its tiles fit,
+        no chunks), with the cap in its softmax and the sink and the gates where its key splits are merged."""
         sinks = getattr(self, "sinks", None)
         softcap = float(getattr(self, "softcap", 0.0) or 0.0)
         plan = ctx.plans.get((self.PLAN,)) if not self.rt.is_fp32 else None
 
         def through_the_pages(token_seq):
+            if (pages is not None and not latent and not self.chunk and q.dtype == torch.bfloat16
+                    and out.dtype == torch.bfloat16 and q.shape[2] == out.shape[2]
+                    and q.shape[2] in ops.DECODE_HEAD_DIMS and ops.tile_pages(pages.shape[3])):
+                ops.decode_attention(q, pages, bt, token_seq, ctx.positions, out, self.window, self.scale,
+                                     softcap=softcap, sink=sinks, gate=gate, status=ctx.status)
+                return
             # (the kernel that reads a key once for all heads of its group wants rows of whole 16-byte pieces)
             if ops.grouped_attention_ok(cache.dtype, q.shape[2], out.shape[2]):
                 ops.grouped_attention(q, cache, bt, token_seq, ctx.positions, out, self.window, self.scale,

@@ -158,5 +158,6 @@ class NormedAttention(PortionAttention, Mixer):
                               pos.magnitude, ctx.positions, ctx.token_seq, bt, q, kv, G, dv, P, status=ctx.status,
                               bias=self.bias, whole=self.norm_whole)
         out = torch.empty((T, H, dv), dtype=rt.dtype, device=x.device)
-        self.attend(q, kv, bt, ctx, out, kv_heads=G, page_tokens=P, gate=full[:, C:] if self.out_gate else None)
+        self.attend(q, kv, bt, ctx, out, kv_heads=G, page_tokens=P, gate=full[:, C:] if self.out_gate else None,
+                    pages=pages.kv if pages.kv.dim() == 5 else None)
         return self.o.f32_sums(out.view(T, H * dv))

@@ -1129,8 +1129,15 @@ def tabopel_kernels(width, heads, kv_heads, ff, T, batch, context):
                    lambda: ops.grouped_attention(qo, pages, bt, seq, positions, ao, None, d ** -0.5, kv_heads=G, page_tokens=P, sink=sink, softcap=50.0), kvb)
             report("grouped_attention (all keys, zero sink, gates in the merge)",
                    lambda: ops.grouped_attention(qo, pages, bt, seq, positions, ao, None, d ** -0.5, kv_heads=G, page_tokens=P, sink=torch.zeros_like(sink), gate=proj[:, C:]), kvb)
+            p5 = pages.view(-1, 2, G, P, d)
+            report("decode_attention (copy engine; soft cap, learned sink in the merge)",
+                   lambda: ops.decode_attention(qo, p5, bt, seq, positions, ao, None, d ** -0.5, softcap=50.0, sink=sink), kvb)
+            report("decode_attention (copy engine; zero sink and gates in the merge)",
+                   lambda: ops.decode_attention(qo, p5, bt, seq, positions, ao, None, d ** -0.5, sink=torch.zeros_like(sink), gate=proj[:, C:]), kvb)
+            report("  Qwen2: decode_attention (copy engine)",
+                   lambda: ops.decode_attention(qo, p5, bt, seq, positions, ao, None, d ** -0.5), kvb)
             report("  Tomodra: grouped_attention (chunk of 1,024, sink)",
-                   lambda: ops.grouped_attention(qo, pages, bt, seq, positions, ao, None, d ** -0.5, kv_heads=G, page_tokens=P, chunk=1024, sink=sink), kvb // 2)
+                   lambda: ops.grouped_attention(qo, pages, bt, seq, positions - 1, ao, None, d ** -0.5, kv_heads=G, page_tokens=P, chunk=1024, sink=sink), kvb // 2)
         # ---- retention beside gated linear attention (the same scan with a decay per channel)
         rq = torch.randn(N, 3 * H * d, device=dev)
         state = torch.zeros(S, H, d, d, device=dev)
