@@ -149,11 +149,21 @@ qk_normed_prepare_kernel(const float* __restrict__ proj, int ld, const float* __
     __syncthreads();
     float whole_q = 1.f, whole_k = 1.f;
     if (whole && q_w) {      // one scale for all heads of q and one for all heads of k
+        // (four loads of a thread under way at once: the sums are a chain of latencies otherwise)
         float sq = 0.f, sk = 0.f;
-        for (int i = threadIdx.x; i < (H + G) * dk; i += blockDim.x) {
-            const float v = in[i] + (bias ? bias[i] : 0.f);
-            if (i < H * dk) sq = fmaf(v, v, sq);
-            else sk = fmaf(v, v, sk);
+        const int n = (H + G) * dk, step = blockDim.x;
+        for (int i0 = threadIdx.x; i0 < n; i0 += 4 * step) {
+            float v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * step;
+                v[u] = i < n ? in[i] + (bias ? bias[i] : 0.f) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (i0 + u * step < H * dk) sq = fmaf(v[u], v[u], sq);
+                else sk = fmaf(v[u], v[u], sk);
+            }
         }
         whole_q = 1.f / sqrtf(block_sum(sq, scratch) / (float)(H * dk) + eps);
         whole_k = 1.f / sqrtf(block_sum(sk, scratch) / (float)(G * dk) + eps);
