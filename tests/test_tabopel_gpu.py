@@ -149,6 +149,10 @@ ATTENTION_CASES = [
     ("attention_2", 1, 1, 32, 40, 0, 0.0, tu.rot(32, 10000.0), 16),
     ("attention_2", 2, 1, 128, 64, 0, 6.0, tu.rot(64, 10000.0), 64),
     ("attention_2", 2, 2, 14, 10, 0, 4.0, tu.rot(2, 10000.0), 16),
+    # keys and values of one size that the copy-engine decode kernel takes: cap, learned sink (and above: zero sink, gates)
+    ("attention_2", 4, 2, 128, 128, 0, 6.0, tu.rot(64, 10000.0), 64),
+    ("attention_2", 2, 2, 64, 64, 0, 4.0, tu.rot(32, 500.0), 16),
+    ("attention", 8, 1, 128, 128, 4, 0.0, tu.rot(128, 500000.0, (8.0, 1.0, 4.0, 256)), 32),
 ]
 
 
