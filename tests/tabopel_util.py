@@ -71,6 +71,8 @@ def config(vocab, width, eps, scale, loop, layers):
 #    convolution of five taps; no identity expert; twelve experts of which five are taken.
 # D: no size is a multiple of 4 (width, heads' sizes, ff): the kernels' roads of one element per access; two identity
 #    experts of three; a convolution of two taps.
+# E: heads of 64 and 128 with keys and values of one size on pages of 64, as large models have them: single tokens
+#    attend through the copy-engine decode kernel (zero sink and gates, cap and learned sinks); the first layer routes.
 CONFIGS = {
     "A": config(211, 72, 1e-5, 3.0, (0, 2, 3), [
         moe(retention(3, 20, 12, (0.9, 0.99, 0.9990234375), rot(8, 10000.0)), 5, 1, 2, 40),
@@ -91,8 +93,13 @@ CONFIGS = {
         dense(conv_attention(3, 1, 10, 6, 0.3, 2, rot(6, 1000.0)), 50),
         moe(retention(3, 10, 6, (0.8, 0.95, 0.99), rot(10, 10000.0)), 1, 2, 2, 30),
         dense(normed_attention(2, 2, 14, 10, 0.25, 4.0, rot(2, 10000.0)), 34)]),
+    "E": config(300, 256, 1e-6, 10.0, (1, 3, 2), [
+        moe(conv_attention(8, 2, 64, 64, 0.125, 4, rot(64, 500000.0, (8.0, 1.0, 4.0, 128))), 6, 2, 3, 96),
+        dense(normed_attention(4, 4, 128, 128, 0.09, 8.0, rot(64, 10000.0)), 384),
+        moe(retention(4, 64, 64, (0.96875, 0.984375, 0.9921875, 0.998046875), rot(64, 1000000.0)), 3, 1, 2, 128),
+        dense(conv_attention(4, 1, 128, 128, 0.09, 2, rot(128, 10000.0)), 320)]),
 }
-SEEDS = {"A": 41, "B": 42, "C": 43, "D": 44}
+SEEDS = {"A": 41, "B": 42, "C": 43, "D": 44, "E": 45}
 
 
 def random_config(seed):
