@@ -117,7 +117,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tiles,
                             int n_pairs, const int* __restrict__ segments, int n_slots, float* __restrict__ part_o,
                             float2* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int H, int K, int P,
-                            int window, float scale_log2, float cap, float cap_pre, int* __restrict__ status) {
+                            int window, float scale_log2, float cap, float cap_pre, int* __restrict__ status,
+                            const float* __restrict__ sink) {
+    // sink (or null): float32 [H]; one more term exp(sink[h]) in the softmax's denominator, which has no key and no
+    // value: it joins a row's sum where the row is normalised (here, or where its segments are merged)
     // cap > 0: a score s becomes cap * tanh(s * cap_pre) (cap_pre = scale / cap) and scale_log2 is log2(e) alone
     constexpr int SUB = D / 64;                            // 64-column (128-byte) sub-tiles per row
     constexpr int Q_BYTES = SUB * AT_BM * 128;             // one row tile of Q
@@ -490,7 +493,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
                 if (r < me.count) part_ml[row + r] = make_float2(m, l);
             } else {
-                const float inv = l > 0.f ? 1.f / l : 0.f;
+                const float total = sink && l > 0.f ? l + exp2f(sink[h] * 1.4426950408889634f - m) : l;
+                const float inv = total > 0.f ? 1.f / total : 0.f;
 #pragma unroll
                 for (int c = 0; c < D; c += 32) {
                     uint32_t ov[32];
@@ -532,7 +536,8 @@ template <int D>
 __global__ void __launch_bounds__(256)
 prefill_combine_kernel(const int* __restrict__ tiles, int n_pairs, const int* __restrict__ items, int n_slots,
                        const float* __restrict__ part_o, const float2* __restrict__ part_ml,
-                       __nv_bfloat16* __restrict__ out, int H, int* __restrict__ status) {
+                       __nv_bfloat16* __restrict__ out, int H, int* __restrict__ status,
+                       const float* __restrict__ sink) {
     constexpr int CP = D / 32;
     constexpr int ROWS = AT_ROW_TILES * AT_BM;
     pdl_enter(TR_ATT_COMBINE);
@@ -587,6 +592,7 @@ prefill_combine_kernel(const int* __restrict__ tiles, int n_pairs, const int* __
             }
         }
     }
+    if (sink && weight > 0.f) weight += exp2f(sink[h] * 1.4426950408889634f - top);      // the sink's term, once
     const float inv = weight > 0.f ? 1.f / weight : 0.f;
     __nv_bfloat16* dst = out + ((size_t)(tok0 + r) * H + h) * D + lane * CP;
 #pragma unroll
@@ -602,7 +608,7 @@ template <int D>
 int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mc, const int* block_table, int max_blocks,
                       const int* tiles, int n_tiles, const int* segments, int n_segments, const int* items, int n_items,
                       int n_slots, float* part_o, float* part_ml, void* out, int H, int K, int P, int window, float scale,
-                      float softcap, int* status, cudaStream_t stream) {
+                      float softcap, int* status, cudaStream_t stream, const float* sink = nullptr) {
     // (more than half of an SM's shared memory, so that two blocks never share its tensor memory)
     size_t smem = 1024 + (size_t)AT_ROW_TILES * (D / 64) * AT_BM * 128 +
                   (size_t)AT_STAGES * 2 * (D / 64) * AT_BN * 128 + 256;
@@ -615,10 +621,10 @@ int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mc, const int* b
     int rc = launch(kernel, grid, AT_THREADS, smem, stream, mq, mc, block_table, max_blocks, tiles, n_pairs, segments,
                     n_slots, part_o, (float2*)part_ml, (__nv_bfloat16*)out, H, K, P, window,
                     (softcap > 0.f ? 1.f : scale) * 1.4426950408889634f, softcap > 0.f ? softcap : 0.f,
-                    softcap > 0.f ? scale / softcap : 0.f, status);
+                    softcap > 0.f ? scale / softcap : 0.f, status, sink);
     if (rc || !segments || n_items <= 0) return rc;
     return launch(prefill_combine_kernel<D>, dim3(n_items, AT_ROW_TILES * AT_BM / 8), 256, 0, stream, tiles, n_pairs,
-                  items, n_slots, (const float*)part_o, (const float2*)part_ml, (__nv_bfloat16*)out, H, status);
+                  items, n_slots, (const float*)part_o, (const float2*)part_ml, (__nv_bfloat16*)out, H, status, sink);
 }
 
 }  // namespace air
@@ -627,11 +633,11 @@ int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mc, const int* b
 // softcap > 0: scores are scale * q.k, then softcap * tanh(score / softcap).
 // segments (or null: one block per pair and head) [n_segments, 5], items [n_items, 4], part_o float32
 // [n_slots, 256, D] and part_ml float32 [n_slots, 256, 2]: see the head of this file.
-AIR_API int air_prefill_attention_tc(const void* q, int T, const void* cache, long long pages, const int* block_table,
-                                     int max_blocks, const int* tiles, int n_tiles, const int* segments, int n_segments,
-                                     const int* items, int n_items, int n_slots, float* part_o, float* part_ml,
-                                     void* out, int H, int K, int D, int P, int window, float scale, float softcap,
-                                     int* status, cudaStream_t stream) {
+static int prefill_attention_tc_any(const void* q, int T, const void* cache, long long pages, const int* block_table,
+                                    int max_blocks, const int* tiles, int n_tiles, const int* segments, int n_segments,
+                                    const int* items, int n_items, int n_slots, float* part_o, float* part_ml,
+                                    void* out, int H, int K, int D, int P, int window, float scale, float softcap,
+                                    int* status, const float* sink, cudaStream_t stream) {
     using namespace air;
     if (n_tiles <= 0) return 0;
     if (segments && (n_segments <= 0 || n_items < 0 || n_slots < 0 || (n_items > 0 && !items) ||
@@ -648,9 +654,31 @@ AIR_API int air_prefill_attention_tc(const void* q, int T, const void* cache, lo
     if (rc) return rc;
     if (D == 64)
         return launch_prefill_tc<64>(mq, mc, block_table, max_blocks, tiles, n_tiles, segments, n_segments, items, n_items,
-                                     n_slots, part_o, part_ml, out, H, K, P, window, scale, softcap, status, stream);
+                                     n_slots, part_o, part_ml, out, H, K, P, window, scale, softcap, status, stream, sink);
     return launch_prefill_tc<128>(mq, mc, block_table, max_blocks, tiles, n_tiles, segments, n_segments, items, n_items,
-                                  n_slots, part_o, part_ml, out, H, K, P, window, scale, softcap, status, stream);
+                                  n_slots, part_o, part_ml, out, H, K, P, window, scale, softcap, status, stream, sink);
+}
+
+AIR_API int air_prefill_attention_tc(const void* q, int T, const void* cache, long long pages, const int* block_table,
+                                     int max_blocks, const int* tiles, int n_tiles, const int* segments, int n_segments,
+                                     const int* items, int n_items, int n_slots, float* part_o, float* part_ml,
+                                     void* out, int H, int K, int D, int P, int window, float scale, float softcap,
+                                     int* status, cudaStream_t stream) {
+    return prefill_attention_tc_any(q, T, cache, pages, block_table, max_blocks, tiles, n_tiles, segments, n_segments,
+                                    items, n_items, n_slots, part_o, part_ml, out, H, K, D, P, window, scale, softcap,
+                                    status, nullptr, stream);
+}
+
+// The same with one more term exp(sink[h]) in every head's softmax denominator (sink float32 [H]).
+AIR_API int air_prefill_attention_tc_sink(const void* q, int T, const void* cache, long long pages,
+                                          const int* block_table, int max_blocks, const int* tiles, int n_tiles,
+                                          const int* segments, int n_segments, const int* items, int n_items,
+                                          int n_slots, float* part_o, float* part_ml, void* out, int H, int K, int D,
+                                          int P, int window, float scale, float softcap, int* status,
+                                          const float* sink, cudaStream_t stream) {
+    return prefill_attention_tc_any(q, T, cache, pages, block_table, max_blocks, tiles, n_tiles, segments, n_segments,
+                                    items, n_items, n_slots, part_o, part_ml, out, H, K, D, P, window, scale, softcap,
+                                    status, sink, stream);
 }
 
 AIR_API int air_trace_set_attention_prefill_tc(unsigned long long* buffer) { return air::set_trace_here(buffer); }

@@ -101,6 +101,9 @@ _SIGNATURES = {
     "air_prefill_attention_tc": [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
                                  c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                  c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p],
+    "air_prefill_attention_tc_sink": [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                      c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                      c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p],
     "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                    c_void_p, c_void_p],
 }
@@ -1324,10 +1327,10 @@ def prefill_attention_scratch(slots: int, head_dim: int, device):
 
 
 def prefill_attention_tc(q, cache, block_table, tiles, out, window, scale, status=None, segments=None, items=None,
-                         slots=0, scratch=None, softcap=0.0):
+                         slots=0, scratch=None, softcap=0.0, sink=None):
     """bfloat16 causal attention with both products on the tcgen05 tensor cores (see
     attention_prefill_tc.cu); arguments as prefill_attention; head size 64 or 128.  softcap > 0: score = softcap *
-    tanh(scale * q.k / softcap).
+    tanh(scale * q.k / softcap).  sink (float32 [H]): one more term exp(sink[h]) in the softmax's denominator.
     segments [n, 5] int32 (pair of the list, head, first key tile, key tiles, slot or -1): which block takes which
     part of which pair's stream of keys, instead of one block per pair and head; items [m, 4] int32 (pair, head,
     first slot, slots): the (pair, head)s whose segments write partial sums into `slots` slots, merged here.
@@ -1359,10 +1362,14 @@ def prefill_attention_tc(q, cache, block_table, tiles, out, window, scale, statu
             _req(part_ml, "scratch[1]", (torch.float32,), (None, 2 * TILE_GROUP * 16, 2))
             if part_o.shape[0] < slots or part_ml.shape[0] < slots:
                 raise KernelError("prefill_attention_tc: the scratch tensors hold fewer slots than the segments name")
-    _check(_get("air_prefill_attention_tc")(
-        q.data_ptr(), T, cache.data_ptr(), cache.shape[0], block_table.data_ptr(), block_table.shape[1],
-        tiles.data_ptr(), tiles.shape[0], _ptr(segments), 0 if segments is None else segments.shape[0],
-        _ptr(items) if n_items else None, n_items, int(slots) if segments is not None else 0, _ptr(part_o), _ptr(part_ml),
-        out.data_ptr(), H, K, d, P, int(window or 0), float(scale), float(softcap or 0.0), _ptr(status), _stream()),
-        "prefill_attention_tc")
+    args = (q.data_ptr(), T, cache.data_ptr(), cache.shape[0], block_table.data_ptr(), block_table.shape[1],
+            tiles.data_ptr(), tiles.shape[0], _ptr(segments), 0 if segments is None else segments.shape[0],
+            _ptr(items) if n_items else None, n_items, int(slots) if segments is not None else 0, _ptr(part_o),
+            _ptr(part_ml), out.data_ptr(), H, K, d, P, int(window or 0), float(scale), float(softcap or 0.0),
+            _ptr(status))
+    if sink is not None:
+        _req(sink, "sink", (torch.float32,), (H,))
+        _check(_get("air_prefill_attention_tc_sink")(*args, sink.data_ptr(), _stream()), "prefill_attention_tc")
+    else:
+        _check(_get("air_prefill_attention_tc")(*args, _stream()), "prefill_attention_tc")
     return out

@@ -6,6 +6,7 @@ import torch
 from ..config.model_config import ConfigError
 from ..csrc import ops
 from ..weights.loader import TensorSpec
+from .attention import TiledAttention
 from .base import Mixer, PagedKV, SlotState
 from .gathered_attention import PortionAttention
 from .linear import Linear
@@ -45,7 +46,11 @@ class NormedAttention(PortionAttention, Mixer):
 
     q, k and v are one product; one kernel then normalises, rotates and writes keys and values to the pages; pages of a
     chunk that no later query can see go back to the pool.  Prompt portions attend through matrix products over their
-    gathered keys, everything else through the 32-bit kernel that reads the pages (PortionAttention)."""
+    gathered keys, everything else through the 32-bit kernel that reads the pages (PortionAttention).  Where keys and
+    values have one size of 64 or 128, the pages fit the tile kernels and there are no chunks, a bfloat16 engine takes
+    the dense decoder's roads instead (TiledAttention's plan of a step's tiles): prompt portions the tcgen05 kernel,
+    single tokens the copy-engine kernel, both with the cap in their softmax and the sink's term where a row is
+    normalised; the output gates multiply where the decode kernel's key splits are merged, or in a kernel of their own."""
 
     graph_safe = True
 
@@ -76,6 +81,36 @@ class NormedAttention(PortionAttention, Mixer):
                                              "even key sizes, and sizes up to 256")
         pos = p["position"]
         self.position = POSITION_ENCODINGS.get(pos.kind)(pos)
+
+    def tiles_fit(self) -> bool:
+        """Whether this layer's attention runs on the dense decoder's tile kernels (see the class's text)."""
+        return (self.rt.dtype == torch.bfloat16 and self.head_dim == self.v_dim and not self.chunk
+                and self.head_dim in ops.TC_ATTENTION_HEAD_DIMS and ops.tile_pages(self.rt.page_tokens))
+
+    def plan_key(self):
+        return TiledAttention.plan_key(self) if self.tiles_fit() else PortionAttention.plan_key(self)
+
+    def plan(self, batch):
+        return TiledAttention.plan(self, batch) if self.tiles_fit() else PortionAttention.plan(self, batch)
+
+    def attend_tiles(self, q, kv, bt, ctx, out, plan, gate):
+        """The step's attention on the tile kernels: the single next tokens at the head of the batch through the
+        copy-engine decode kernel, the other entries through the tcgen05 kernel; kv [pages, 2, K, P, d]."""
+        T, H, d = q.shape
+        n = plan.decode_prefix
+        if n:
+            ops.decode_attention(q[:n], kv, bt, ctx.token_seq[:n], ctx.positions[:n], out[:n], self.window, self.scale,
+                                 softcap=self.softcap, sink=self.sinks, gate=None if gate is None else gate[:n],
+                                 status=ctx.status)
+        if plan.tiles.shape[0]:
+            if plan.slots and getattr(plan, "scratch", None) is None:
+                plan.scratch = ops.prefill_attention_scratch(plan.slots, d, q.device)
+            ops.prefill_attention_tc(q, kv, bt, plan.tiles, out, self.window, self.scale, status=ctx.status,
+                                     segments=plan.segments, items=plan.items, slots=plan.slots,
+                                     scratch=getattr(plan, "scratch", None), softcap=self.softcap, sink=self.sinks)
+            if gate is not None and T > n:
+                ops.sigmoid_gate(out[n:].view(T - n, H * d), gate[n:], ctx.token_seq[n:])
+        return out
 
     @property
     def channels(self):
@@ -158,6 +193,11 @@ class NormedAttention(PortionAttention, Mixer):
                               pos.magnitude, ctx.positions, ctx.token_seq, bt, q, kv, G, dv, P, status=ctx.status,
                               bias=self.bias, whole=self.norm_whole)
         out = torch.empty((T, H, dv), dtype=rt.dtype, device=x.device)
-        self.attend(q, kv, bt, ctx, out, kv_heads=G, page_tokens=P, gate=full[:, C:] if self.out_gate else None,
-                    pages=pages.kv if pages.kv.dim() == 5 else None)
+        gate = full[:, C:] if self.out_gate else None
+        plan = ctx.plans.get(TiledAttention.plan_key(self)) if self.tiles_fit() and not ctx.all_decode else None
+        if plan is not None:
+            self.attend_tiles(q, pages.kv, bt, ctx, out, plan, gate)
+        else:
+            self.attend(q, kv, bt, ctx, out, kv_heads=G, page_tokens=P, gate=gate,
+                        pages=pages.kv if pages.kv.dim() == 5 else None)
         return self.o.f32_sums(out.view(T, H * dv))

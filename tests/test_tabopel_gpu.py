@@ -193,15 +193,17 @@ def test_attention_mixers_through_portions_and_single_tokens(kind, H, G, d, dv, 
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("kind,cap", [("attention", 0.0), ("attention_2", 40.0)])
-def test_attention_finds_a_key_far_away_and_at_page_borders(kind, cap, dtype):
+@pytest.mark.parametrize("kind,cap,d,E", [("attention", 0.0, 16, 64), ("attention_2", 40.0, 16, 64),
+                                          ("attention", 0.0, 64, 256), ("attention_2", 40.0, 128, 512)])
+def test_attention_finds_a_key_far_away_and_at_page_borders(kind, cap, d, E, dtype):
     """Keys and queries are made by hand: late queries point at the keys of tokens 0, 15, 16, 17 and 200 (a score that
     stands out among hundreds; the query is the key turned back by the distance between them), and the values show
     which key was found.  As one prompt, as a prompt with decoded tokens and in ragged portions, over pages of 16 that
-    are scattered."""
+    are scattered.  Heads of 64 and 128 take the tile kernels in bfloat16 (tcgen05 for portions, the copy engine's for
+    single tokens), the others the kernels that read the pages in 32-bit."""
     from air_b200.cache.manager import CacheManager
-    E, H, G, d, dv, T, scale, eps = 64, 2, 1, 16, 16, 420, 0.25, 1e-6
-    r = tu.rot(8, 10000.0)
+    H, G, dv, T, scale, eps = 2, 1, d, 420, 0.25 * (16 / d) ** 0.5, 1e-6
+    r = tu.rot(d // 2, 10000.0)
     rng = np.random.default_rng(5)
     w = attention_weights(rng, E, H, G, d, dv, scale, kind, 0, dtype)
     if kind == "attention_2":      # queries and keys as they are projected: no bias, the norm's weight the same everywhere
