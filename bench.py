@@ -1120,6 +1120,20 @@ def tabopel_kernels(width, heads, kv_heads, ff, T, batch, context):
         gate_h = torch.rand(N, H, device=dev)
         report("sigmoid_gate (a logit per output element)", lambda: ops.sigmoid_gate(out.view(N, H * d), proj[:, C:], seq), N * H * d * 8)
         report("  Bivizen: head_gate (a gate per head)", lambda: ops.head_gate(out, gate_h, seq), N * H * d * 4)
+        if label == "prompt":
+            # ---- a prompt's attention on the tcgen05 kernel with the cap and the sink, beside the dense decoder's
+            from air_b200.parts.attention import TiledAttention
+            from air_b200.parts.base import HostBatch
+            planner = type("P", (TiledAttention,), {"heads": H, "window": None})()
+            plan = planner.plan(HostBatch(counts=[T], lengths=[0], slots=[0], q_start=[0, T]))
+            tiles_ = i32(plan.arrays["tiles"].tolist())
+            p5, ao, sk = pages.view(-1, 2, G, P, d), torch.empty(N, H, d, dtype=bf, device=dev), torch.randn(H, device=dev)
+            fl = 4 * H * d * (T * (T + 1) // 2)
+            report("prefill_attention_tc with a soft cap and learned sinks",
+                   lambda: ops.prefill_attention_tc(qo, p5, bt, tiles_, ao, None, d ** -0.5, softcap=50.0, sink=sk), flops=fl)
+            report("prefill_attention_tc with a zero sink",
+                   lambda: ops.prefill_attention_tc(qo, p5, bt, tiles_, ao, None, d ** -0.5, sink=torch.zeros_like(sk)), flops=fl)
+            report("  Qwen2: prefill_attention_tc", lambda: ops.prefill_attention_tc(qo, p5, bt, tiles_, ao, None, d ** -0.5), flops=fl)
         if label == "decode":
             # ---- single tokens over the pages: cap and sink, and the gate in the merge, beside Tomodra's chunk and sink
             sink = torch.randn(H, device=dev)
