@@ -171,9 +171,7 @@ class SandwichBlock(Block):
             raise ops.KernelError("sandwich: the sub-layer must return its output as a tensor or as partial sums")
         if delta.dtype != torch.float32:
             delta = ops.convert(delta, torch.empty(delta.shape, dtype=torch.float32, device=delta.device))
-        w = norm.weight if norm.weight.dtype == torch.float32 else norm.weight.to(torch.float32)
-        norm.weight = w
-        return NormedSum(delta, w, norm.eps)
+        return NormedSum(delta, norm.weight_f32(), norm.eps)
 
     def forward(self, h, pending, ctx, cache, owns_cache=True):
         ctx.residual = None          # a sub-layer's output is normalised before it is added: the parts return it

@@ -26,8 +26,17 @@ class RMSNorm(Norm):
         super().load(tensors, rt)
         self.weight = tensors[self.prefix + self.spec.get("tensor", "weight")]
         self.eps = float(self.spec["eps"])
+        self.weight_f32()
 
     prenorm = True      # x * scale(row) * w: forward_prenormed writes bfloat16(x * w) and leaves the scale to the consumer
+
+    def weight_f32(self) -> torch.Tensor:
+        """The weight in float32 (made once), for the kernels that take it so."""
+        src = self.weight
+        if getattr(self, "_weight_f32_of", None) is not src:
+            self._weight_f32 = src if src.dtype == torch.float32 else src.to(torch.float32)
+            self._weight_f32_of = src
+        return self._weight_f32
 
     @staticmethod
     def _as_terms(delta):
@@ -49,9 +58,8 @@ class RMSNorm(Norm):
         if isinstance(delta, NormedSum):
             # a sub-layer's output with a norm of its own behind it: one kernel takes that norm, completes the stream
             # and normalises it
-            if self.weight.dtype != torch.float32:
-                self.weight = self.weight.to(torch.float32)
-            return ops.normed_add_norm(h, delta.term, delta.weight, delta.eps, self.weight, self.eps, out, rows=rows)
+            return ops.normed_add_norm(h, delta.term, delta.weight, delta.eps, self.weight_f32(), self.eps, out,
+                                       rows=rows)
         if isinstance(delta, ScaledSum):
             # the outputs of sub-layers that stand side by side, each with its scale per column: one kernel
             # completes the stream with them and normalises
